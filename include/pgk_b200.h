@@ -467,6 +467,59 @@ int pgk_gemv_nvf4_bf16_noalloc(const void* A, const void* B_data, const void* B_
 int pgk_p2p_error(int* host_flag);
 int pgk_p2p_destroy(void);
 
+/* ------------------------------------------------------------------ token-major ("ragged batch") models
+ * net-new: no counterpart in the reference (its models run one sequence on a fixed cache in 16 bits).  Rows are the
+ * tokens of a step -- any mix of prompt portions and single decoded tokens of different sequences -- and every
+ * activation is float32; weight matrices are [N, K] in float32 (dtype code 0) or bfloat16 (2).  seq_gemm.cu,
+ * seq_attention.cu, seq_layers.cu. */
+/* C[m, :] = A[a_rows ? a_rows[m] : m, :] . W[g]^T.  group_off [groups + 1] (or NULL) cuts rows 0 .. group_off[groups] into
+ * consecutive runs, run g uses matrix W + g * w_group_stride (max_rows bounds the longest run).  epilogue 0: plain;
+ * 1: W rows are (gate_j, up_j) pairs, C[m, j] = silu(gate) * up, ldc >= N / 2; 2: c * scale, then cap * tanh(c / cap)
+ * when cap > 0. */
+int pgk_gemm_rows_f32(const float* A, int lda, const int32_t* a_rows, const void* W, int wdt, long long w_group_stride,
+                      float* C, int ldc, int M, int N, int K, const int32_t* group_off, int groups, int max_rows,
+                      int epilogue, float scale, float cap, void* stream);
+/* the same product for few rows (decoding): blocks of rows_per_block (<= 8) consecutive rows share the matrix
+ * row_group[first row of the block] (NULL: matrix 0); the weights are streamed once per block of rows */
+int pgk_gemm_few_rows_f32(const float* A, int lda, const int32_t* a_rows, const void* W, int wdt, long long w_group_stride,
+                          float* C, int ldc, int M, int N, int K, const int32_t* row_group, int rows_per_block,
+                          int epilogue, float scale, float cap, void* stream);
+/* x[t, :] = table[tokens[t], :] */
+int pgk_embed_rows_f32(const void* table, int wdt, const int32_t* tokens, float* x, int n, int width, int vocab, void* stream);
+/* y = base[src_rows ? src_rows[t] : t] (or 0) + sum_k weights[t, k] * parts[inv[t, k]];  r = LayerNorm(y) * gamma + beta;
+ * add != 0: out[t] += r, else out[t] = r */
+int pgk_combine_layernorm_f32(const float* base, const int32_t* src_rows, const float* parts, const int32_t* inv,
+                              const float* weights, int top, const float* gamma, const float* beta, float eps, float* out,
+                              int rows, int width, int add, void* stream);
+/* router: scores = softmax(x . router^T) over all experts; with group_count > 1 only members of the group_keep groups of
+ * neighbours with the largest member score may be chosen; the `top` largest (ties: lowest index) -> idx [tokens, top],
+ * weights = chosen scores / (their sum + 1e-20).  counts (zeroed, or NULL) receives the rows per expert and rank the
+ * arrival number of every (token, slot) at its expert. */
+int pgk_moe_route_grouped(const float* x, int ldx, const void* router, int wdt, int tokens, int width, int experts, int top,
+                          int group_count, int group_keep, int32_t* idx, float* weights, int32_t* rank, int32_t* counts,
+                          void* stream);
+/* offsets [experts + 1] = exclusive scan of counts (cleared afterwards); perm[row] = token of the row, inv[t * top + k] = row */
+int pgk_moe_row_lists(int32_t* counts, int32_t* offsets, const int32_t* idx, const int32_t* rank, int32_t* perm, int32_t* inv,
+                      int experts, int tokens, int top, void* stream);
+/* Paged cache: page p holds K rows [kv_heads][page_size][dim] and V rows [kv_heads][page_size][vdim] (float32 = 0 or
+ * bfloat16 = 2); table [slots][max_pages].  proj rows are [q (heads x dim) | k | v | gate (heads x vdim)].
+ * mixer_prep: RMS norm of q (in place) and k per head, v_mode 1 records v in v_first [tokens, kv_heads x vdim], 2 replaces
+ * v by (1 - lam) v + lam v_first; writes K / V at (slot[t], pos[t]). */
+int pgk_seq_mixer_prep(float* proj, int ld, int tokens, int heads, int kv_heads, int dim, int vdim, const float* q_weight,
+                       const float* k_weight, float eps, int v_mode, float lam, float* v_first, void* k_cache, void* v_cache,
+                       int cache_dtype, const int32_t* table, int max_pages, int page_size, const int32_t* slot,
+                       const int32_t* pos, void* stream);
+/* tiles [n_tiles][4] = (first row, queries <= pgk_seq_queries_per_tile, slot, first position): consecutive positions of one
+ * sequence.  score = scale q.k, cap * tanh(score / cap) when cap > 0, minus slopes[h] * (i - j) when slopes; key j visible
+ * from i when j <= i and (chunk > 0) floor(j / chunk) == floor(i / chunk); out [row, heads x vdim], times
+ * sigmoid(proj[row, gate_off + ...]) when gate != 0. */
+int pgk_seq_attention(const float* proj, int ld, int q_off, int gate_off, float* out, int ldo, const void* k_cache,
+                      const void* v_cache, int cache_dtype, const int32_t* table, int max_pages, int page_size,
+                      const int32_t* tiles, int n_tiles, const float* slopes, int heads, int kv_heads, int dim, int vdim,
+                      int chunk, float scale, float softcap, int gate, void* stream);
+int pgk_seq_heads_per_block(int heads, int kv_heads);
+int pgk_seq_queries_per_tile(int heads, int kv_heads);
+
 #ifdef __cplusplus
 }
 #endif

@@ -114,12 +114,23 @@ _SIGS = {
     "pgk_p2p_create": [i32, i32, vp], "pgk_p2p_open": [vp], "pgk_p2p_allreduce_add_bf16": [vp, vp, vp, sz, vp],
     "pgk_p2p_ll_allreduce_add_bf16": [vp, vp, vp, sz, vp], "pgk_p2p_ll_argmax_bf16": [vp, vp, i32, vp],
     "pgk_p2p_error": [vp], "pgk_p2p_destroy": [],
+    # token-major models (seq_gemm.cu, seq_attention.cu, seq_layers.cu)
+    "pgk_gemm_rows_f32": [vp, i32, vp, vp, i32, C.c_longlong, vp, i32, i32, i32, i32, vp, i32, i32, i32, f32, f32, vp],
+    "pgk_gemm_few_rows_f32": [vp, i32, vp, vp, i32, C.c_longlong, vp, i32, i32, i32, i32, vp, i32, i32, f32, f32, vp],
+    "pgk_embed_rows_f32": [vp, i32, vp, vp, i32, i32, i32, vp],
+    "pgk_combine_layernorm_f32": [vp, vp, vp, vp, vp, i32, vp, vp, f32, vp, i32, i32, i32, vp],
+    "pgk_moe_route_grouped": [vp, i32, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp],
+    "pgk_moe_row_lists": [vp, vp, vp, vp, vp, vp, i32, i32, i32, vp],
+    "pgk_seq_mixer_prep": [vp, i32, i32, i32, i32, i32, i32, vp, vp, f32, i32, f32, vp, vp, vp, i32, vp, i32, i32, vp, vp, vp],
+    "pgk_seq_attention": [vp, i32, i32, i32, vp, i32, vp, vp, i32, vp, i32, i32, vp, i32, vp, i32, i32, i32, i32, i32, f32,
+                          f32, i32, vp],
 }
 _RESTYPE = {"pgk_last_error": C.c_char_p, "pgk_launch_count": i64, "pgk_launch_count_reset": None,
             "pgk_sdpa_workspace_bytes": sz, "pgk_p2p_handle_bytes": sz, "pgk_p2p_ready": i32,
-            "pgk_p2p_max_bytes": sz}
+            "pgk_p2p_max_bytes": sz, "pgk_seq_heads_per_block": i32, "pgk_seq_queries_per_tile": i32}
 _EXTRA = {"pgk_last_error": [], "pgk_launch_count": [], "pgk_launch_count_reset": [],
-          "pgk_sdpa_workspace_bytes": [i32, i32, i32, i32], "pgk_p2p_handle_bytes": [], "pgk_p2p_ready": [], "pgk_p2p_max_bytes": []}
+          "pgk_sdpa_workspace_bytes": [i32, i32, i32, i32], "pgk_p2p_handle_bytes": [], "pgk_p2p_ready": [], "pgk_p2p_max_bytes": [],
+          "pgk_seq_heads_per_block": [i32, i32], "pgk_seq_queries_per_tile": [i32, i32]}
 
 
 def load() -> C.CDLL:
@@ -132,14 +143,18 @@ def load() -> C.CDLL:
             f"pygpukit_b200: native library {LIB_PATH} not found. Build it with "
             "`python -m pygpukit_b200.build` (needs nvcc); there is no CPU fallback on this path.")
     lib = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
+    # a library built from a subset of the sources (build.py, `components`) exports a subset of the symbols: the ones
+    # that are missing stay unbound and raise when they are called
     for name, args in _SIGS.items():
-        fn = getattr(lib, name)
-        fn.argtypes = args
-        fn.restype = i32
+        fn = getattr(lib, name, None)
+        if fn is not None:
+            fn.argtypes = args
+            fn.restype = i32
     for name, args in _EXTRA.items():
-        fn = getattr(lib, name)
-        fn.argtypes = args
-        fn.restype = _RESTYPE[name]
+        fn = getattr(lib, name, None)
+        if fn is not None:
+            fn.argtypes = args
+            fn.restype = _RESTYPE[name]
     _lib = lib
     return lib
 
@@ -162,8 +177,11 @@ class _Api:
     """lib.<fn>(...) with automatic error checking: `api.gemv_fp8_bf16(...)`."""
 
     def __getattr__(self, name: str):
-        fn = getattr(load(), "pgk_" + name)
-        if fn.restype is i32 and name != "version":
+        fn = getattr(load(), "pgk_" + name, None)
+        if fn is None:
+            raise RuntimeError(f"pgk_{name} is not in {LIB_PATH}: it was built from a subset of the sources; run "
+                               "`python -m pygpukit_b200.build` for the whole library")
+        if fn.restype is i32 and name != "version" and ("pgk_" + name) not in _EXTRA:
             def call(*a, _fn=fn):
                 check(_fn(*a))
             call.__name__ = name

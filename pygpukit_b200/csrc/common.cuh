@@ -37,6 +37,7 @@ struct GemvXchg {
 };
 bool p2p_gemv_xchg(GemvXchg* x);     // p2p.cu: false until the peer buffers are open
 void fp8_codes_forget(const void* base);
+void set_free_hook(void (*fn)(const void*));   // runtime.cu: called by pgk_free() with the pointer being released
 
 
 #define PGK_CUDA(call)                                                        \

@@ -90,6 +90,7 @@ void fp8_codes_forget(const void* base) {
     std::lock_guard<std::mutex> lk(g_scan_mu);
     g_scan_clean.erase(base);
 }
+static const bool g_free_hook_registered = (set_free_hook(fp8_codes_forget), true);
 
 // NMAT = 1: plain GEMV; NMAT = 2: gate/up pair with SiLU*up epilogue.
 //

@@ -32,6 +32,11 @@ int cuda_fail(cudaError_t e, const char* what, const char* file, int line) {
     return (int)e ? (int)e : 1;
 }
 
+// pgk_free() tells interested translation units that an allocation is gone (the FP8 code scanner remembers base
+// pointers); registered at load time, so runtime.cu links without them
+static void (*g_free_hook)(const void*) = nullptr;
+void set_free_hook(void (*fn)(const void*)) { g_free_hook = fn; }
+
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 bool pdl_enabled() { return g_pdl.load(std::memory_order_relaxed) != 0; }
 
@@ -102,7 +107,7 @@ int pgk_malloc(void** ptr, size_t bytes) {
 }
 int pgk_free(void* ptr) {
     if (ptr) {
-        fp8_codes_forget(ptr);
+        if (g_free_hook) g_free_hook(ptr);
         PGK_CUDA(cudaFree(ptr));
     }
     return 0;

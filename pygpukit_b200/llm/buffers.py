@@ -79,3 +79,40 @@ class PrefillBuffers:
 
 
 __all__ = ["DecodeBuffers", "PrefillBuffers"]
+
+
+class RowBuffers:
+    """Work arrays of the token-major models (llm/models/layered.py), float32 unless noted, sized for `rows` tokens
+    of the widest layer and regrown (never shrunk) when a step brings more."""
+
+    def __init__(self, config, rows: int):
+        from ..core.dtypes import float32
+        W = config.hidden_size
+        proj = attn = gv = top = ff = sff = experts = 1
+        for L in config.layers:
+            m = L.mixer
+            proj = max(proj, m.heads * m.dim + m.kv_heads * m.dim + m.kv_heads * m.vdim + (m.heads * m.vdim if m.out_gate else 0))
+            attn = max(attn, m.heads * m.vdim)
+            gv = max(gv, m.kv_heads * m.vdim)
+            if L.mlp is not None:
+                top, ff, sff = max(top, L.mlp.top), max(ff, L.mlp.ff), max(sff, L.mlp.shared_ff)
+                experts = max(experts, L.mlp.experts)
+        R = self.rows = max(8, int(rows))
+        self.x = GPUArray((R, W), float32)
+        self.y = GPUArray((R, W), float32)
+        self.proj = GPUArray((R, proj), float32)
+        self.attn = GPUArray((R, attn), float32)
+        self.v_first = GPUArray((R, gv), float32)
+        self.moe_idx = GPUArray((R * top,), int32)
+        self.moe_rank = GPUArray((R * top,), int32)
+        self.moe_perm = GPUArray((R * top,), int32)
+        self.moe_inv = GPUArray((R * top,), int32)
+        self.moe_w = GPUArray((R * top,), float32)
+        self.moe_counts = zeros((experts,), int32)          # zero between uses (pgk_moe_row_lists clears it)
+        self.moe_off = GPUArray((experts + 1,), int32)
+        self.moe_act = GPUArray((R * top, ff), float32)
+        self.moe_parts = GPUArray((R * top, W), float32)
+        self.shared_act = GPUArray((R, sff), float32)
+
+
+__all__.append("RowBuffers")

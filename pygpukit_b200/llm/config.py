@@ -226,6 +226,111 @@ def named_config(name: str, max_seq: int = 4096, tp_size: int = 1, tp_rank: int 
     raise ValueError(f"unknown model name {name!r}")
 
 
+
+# ---- per-layer ("layered") configurations: models whose config.json lists every layer with its own mixer and
+# feed-forward (net-new; the reference's families are uniform stacks described by TransformerConfig)
+@dataclass(frozen=True)
+class AttentionMixerSpec:
+    """One attention mixer: H query heads of size `dim`, G key/value heads, values of size `vdim`; score =
+    scale q.k, squashed to softcap tanh(. / softcap) when softcap > 0, minus a per-head distance slope when
+    `distance_bias`; `chunk` > 0 limits a query to the keys of its own chunk of positions; RMS norm on q and k
+    (`qk_norm`), value mixing with the first mixing layer (`v_mix`), sigmoid output gate (`out_gate`)."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    softcap: float = 0.0
+    chunk: int = 0
+    v_mix: bool = False
+    qk_norm: bool = True
+    out_gate: bool = True
+    distance_bias: bool = True
+
+    def slopes(self) -> list[float]:
+        """slope of head h = 2^(-8 (h + 1) / H)"""
+        return [2.0 ** (-8.0 * (h + 1) / self.heads) for h in range(self.heads)] if self.distance_bias else []
+
+
+@dataclass(frozen=True)
+class MoESpec:
+    """Routed experts (gate/up/down, SiLU) + optional shared expert.  Router: softmax over all experts, the `top`
+    best among the members of the `group_keep` best of `group_count` groups of neighbours, weights renormalised."""
+    experts: int
+    top: int
+    ff: int
+    group_count: int = 1
+    group_keep: int = 1
+    shared_ff: int = 0
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    mixer: AttentionMixerSpec
+    mlp: MoESpec | None
+
+
+@dataclass
+class LayeredConfig:
+    """config.json of a layered model.  Every size is read from the file; nothing is assumed equal across layers
+    except the width."""
+    architecture: str
+    vocab_size: int
+    hidden_size: int
+    layers: list[LayerSpec]
+    norm_eps: float = 1e-5
+    logit_scale: float = 1.0
+    logit_softcap: float = 0.0
+
+    @property
+    def num_layers(self) -> int:
+        return len(self.layers)
+
+
+def _dolurax_config(d: dict) -> LayeredConfig:
+    """Dolurax: post-sublayer LayerNorm blocks of chunked, distance-biased, gated attention and a grouped-router MoE."""
+    layers = []
+    for i, L in enumerate(d["layers"]):
+        if L.get("type", "attention") != "attention":
+            raise ValueError(f"Dolurax: layer {i} has unknown type {L.get('type')!r}")
+        m = L["mixer"]
+        mask = m.get("mask") or {}
+        mixer = AttentionMixerSpec(heads=int(m["heads"]), kv_heads=int(m.get("kv_heads") or m["heads"]), dim=int(m["dim"]),
+                                   vdim=int(m.get("vdim") or m["dim"]), scale=float(m["scale"]),
+                                   softcap=float(m.get("softcap") or 0.0), chunk=int(mask.get("size") or 0),
+                                   v_mix=bool(m.get("v_mix", False)))
+        if mixer.heads % mixer.kv_heads:
+            raise ValueError(f"Dolurax: layer {i}: {mixer.heads} heads over {mixer.kv_heads} key/value heads")
+        mlp = None
+        f = L.get("mlp")
+        if f:
+            if f.get("kind", "moe") != "moe":
+                raise ValueError(f"Dolurax: layer {i} has unknown feed-forward kind {f.get('kind')!r}")
+            r = f["router"]
+            g = r.get("groups") or {}
+            sh = f.get("shared") or {}
+            mlp = MoESpec(experts=int(r["experts"]), top=int(r["top"]), ff=int(f["expert"]["ff"]),
+                          group_count=int(g.get("count") or 1), group_keep=int(g.get("keep") or 1),
+                          shared_ff=int(sh.get("ff") or 0))
+            if mlp.experts % mlp.group_count:
+                raise ValueError(f"Dolurax: layer {i}: {mlp.experts} experts do not split into {mlp.group_count} groups")
+        layers.append(LayerSpec(mixer, mlp))
+    return LayeredConfig(architecture="Dolurax", vocab_size=int(d["vocab"]), hidden_size=int(d["width"]), layers=layers,
+                         norm_eps=float((d.get("norm") or {}).get("eps", 1e-5)), logit_scale=float(d.get("logit_scale") or 1.0),
+                         logit_softcap=float(d.get("logit_softcap") or 0.0))
+
+
+# config.json "architecture" -> parser (the model registry of the layered families)
+LAYERED_ARCHITECTURES = {"dolurax": _dolurax_config}
+
+
+def layered_config_from_json(d: dict) -> LayeredConfig | None:
+    """LayeredConfig when config.json names a layered architecture, else None (a uniform Hugging Face config)."""
+    arch = str(d.get("architecture", "")).lower()
+    return LAYERED_ARCHITECTURES[arch](d) if arch in LAYERED_ARCHITECTURES else None
+
+
 __all__ = ["ModelSpec", "TransformerConfig", "GPT2Config", "LlamaConfig", "Qwen3Config", "GPT2_SPEC", "LLAMA_SPEC",
            "QWEN2_SPEC", "QWEN3_SPEC", "QWEN3_MOE_SPEC", "MIXTRAL_SPEC", "MODEL_SPECS", "detect_model_spec",
-           "named_config"]
+           "named_config", "AttentionMixerSpec", "MoESpec", "LayerSpec", "LayeredConfig",
+           "LAYERED_ARCHITECTURES", "layered_config_from_json"]

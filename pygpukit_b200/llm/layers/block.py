@@ -78,4 +78,34 @@ class TransformerBlock:
                 + self.mlp_norm.weight.nbytes)
 
 
-__all__ = ["TransformerBlock"]
+class PostNormBlock:
+    """Block of the token-major models with the norm on the sublayer's OUTPUT: x += LN1(mixer(x)), then
+    x += LN2(ff(x)); both sublayers read the float32 residual stream itself.  Each "norm + add" is one launch that
+    also folds the feed-forward's weighted expert sum and shared expert (pgk_combine_layernorm_f32)."""
+
+    def __init__(self, mixer, norm1: tuple[GPUArray, GPUArray], mlp, norm2: "tuple[GPUArray, GPUArray] | None", eps: float):
+        self.mixer, self.mlp = mixer, mlp
+        self.norm1, self.norm2, self.eps = norm1, norm2, float(eps)
+
+    def forward(self, ctx, x: GPUArray) -> None:
+        from ..._lib import api
+        from ...core.stream import current_stream_handle as _st
+        T, W = ctx.T, x.shape[1]
+        y = ctx.buf.y
+        self.mixer.forward(ctx, x, y)
+        api.combine_layernorm_f32(y.device_ptr, None, None, None, None, 0, self.norm1[0].device_ptr,
+                                  self.norm1[1].device_ptr, self.eps, x.device_ptr, T, W, 1, _st())
+        if self.mlp is not None:
+            base, parts, inv, wts, top = self.mlp.forward(ctx, x, y)
+            api.combine_layernorm_f32(base, None, parts, inv, wts, top, self.norm2[0].device_ptr,
+                                      self.norm2[1].device_ptr, self.eps, x.device_ptr, T, W, 1, _st())
+
+    @property
+    def weight_bytes(self) -> int:
+        n = self.mixer.weight_bytes + 2 * self.norm1[0].nbytes
+        if self.mlp is not None:
+            n += self.mlp.weight_bytes + 2 * self.norm2[0].nbytes
+        return n
+
+
+__all__ = ["TransformerBlock", "PostNormBlock"]

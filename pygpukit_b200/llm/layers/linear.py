@@ -239,4 +239,66 @@ class LinearNVF4:
         return self.data.nbytes + self.scale.nbytes
 
 
-__all__ = ["LinearBF16", "LinearFP8", "LinearNVF4", "Linear", "can_fuse_norm"]
+__all__ = ["LinearBF16", "LinearFP8", "LinearNVF4", "Linear", "can_fuse_norm", "LinearRows", "interleave_gate_up"]
+
+
+class LinearRows:
+    """Linear layer of the token-major models (net-new): float32 activations [rows, K], weights [N, K] (or a stack
+    [E, N, K] of expert matrices) in bfloat16 or float32, float32 accumulation and output.  Many rows run as tiled
+    GEMMs (tensor cores for bfloat16 weights), up to eight rows through the streaming few-row kernel.  epilogue:
+    0 plain, 1 gate/up pairs -> silu(gate) * up (rows of W interleaved by `interleave_gate_up`), 2 scale + tanh cap."""
+
+    FEW = 8
+    FEW_SMEM_FLOATS = 40960          # 160 KB of activations per block
+    FEW_MAX_K = 40960
+
+    def __init__(self, weight: GPUArray, epilogue: int = 0, scale: float = 1.0, cap: float = 0.0):
+        self.weight = weight
+        self.wdt = 2 if weight.dtype == bfloat16 else 0
+        if weight.ndim == 3:
+            self.groups, self.out_features, self.in_features = weight.shape
+        else:
+            self.groups = 1
+            self.out_features, self.in_features = weight.shape
+        self.epilogue, self.scale, self.cap = epilogue, float(scale), float(cap)
+
+    @property
+    def out_cols(self) -> int:
+        return self.out_features // 2 if self.epilogue == 1 else self.out_features
+
+    @property
+    def nbytes(self) -> int:
+        return self.weight.nbytes
+
+    def forward(self, x_ptr: int, ldx: int, rows: int, out_ptr: int, ldo: int, a_rows: int | None = None) -> None:
+        """out[r] = x[a_rows[r] or r] . W^T for `rows` rows (device pointers; a_rows: int32 device array or None)."""
+        N, K = self.out_features, self.in_features
+        if rows <= self.FEW and K <= self.FEW_MAX_K:
+            # rows of one block share the streamed weights; their activations must fit shared memory
+            per_block = max(1, min(rows, self.FEW_SMEM_FLOATS // K))
+            api.gemm_few_rows_f32(x_ptr, ldx, a_rows, self.weight.device_ptr, self.wdt, 0, out_ptr, ldo, rows, N, K, None,
+                                  per_block, self.epilogue, self.scale, self.cap, _st())
+        else:
+            api.gemm_rows_f32(x_ptr, ldx, a_rows, self.weight.device_ptr, self.wdt, 0, out_ptr, ldo, rows, N, K, None, 1,
+                              rows, self.epilogue, self.scale, self.cap, _st())
+
+    def forward_grouped(self, x_ptr: int, ldx: int, out_ptr: int, ldo: int, a_rows: int | None, group_off: int,
+                        max_rows: int) -> None:
+        """Rows sorted by group: run g = rows group_off[g] .. group_off[g + 1] uses matrix g."""
+        N, K = self.out_features, self.in_features
+        api.gemm_rows_f32(x_ptr, ldx, a_rows, self.weight.device_ptr, self.wdt, N * K, out_ptr, ldo, 0, N, K, group_off,
+                          self.groups, max_rows, self.epilogue, self.scale, self.cap, _st())
+
+    def forward_per_row(self, x_ptr: int, ldx: int, rows: int, out_ptr: int, ldo: int, a_rows: int | None,
+                        row_group: int) -> None:
+        """Few rows, each with its own matrix row_group[r] (decoding through a mixture of experts)."""
+        N, K = self.out_features, self.in_features
+        api.gemm_few_rows_f32(x_ptr, ldx, a_rows, self.weight.device_ptr, self.wdt, N * K, out_ptr, ldo, rows, N, K,
+                              row_group, 1, self.epilogue, self.scale, self.cap, _st())
+
+
+def interleave_gate_up(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+    """[F, K] gate and up -> [2 F, K] with gate_j in row 2 j and up_j in row 2 j + 1 (the pair epilogue's layout)."""
+    out = np.empty((2 * gate.shape[0], gate.shape[1]), gate.dtype)
+    out[0::2], out[1::2] = gate, up
+    return out

@@ -1,0 +1,66 @@
+"""Attention mixer of the token-major models on the paged cache (net-new; beside `Attention`, which serves one
+sequence on a fixed cache).  One fused projection [q | k | v | gate], then two launches:
+
+  pgk_seq_mixer_prep   RMS norm of q and k per head, value mixing, K / V rows into the cache pages
+  pgk_seq_attention    scores with scale, tanh cap and per-head distance slopes, chunk mask, softmax, P.V, output gate
+
+and the output projection.  Every constant comes from the `AttentionMixerSpec`; `v_role` says what the layer does
+with its values: 0 nothing, 1 record them as the step's v_first, 2 mix them with the recorded ones.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from ..._lib import api
+from ...core.array import GPUArray
+from ...core.factory import from_numpy
+from ...core.stream import current_stream_handle as _st
+from ..config import AttentionMixerSpec
+from .linear import LinearRows
+
+
+class PagedAttentionMixer:
+    def __init__(self, spec: AttentionMixerSpec, layer: int, qkvg: LinearRows, o_proj: LinearRows, q_norm: GPUArray,
+                 k_norm: GPUArray, eps: float, v_role: int = 0, v_lambda: float = 0.0):
+        self.spec, self.layer = spec, layer
+        self.qkvg, self.o_proj = qkvg, o_proj
+        self.q_norm, self.k_norm, self.eps = q_norm, k_norm, float(eps)
+        self.v_role, self.v_lambda = int(v_role), float(v_lambda)
+        s = spec
+        self.q_cols, self.k_cols, self.v_cols = s.heads * s.dim, s.kv_heads * s.dim, s.kv_heads * s.vdim
+        self.g_cols = s.heads * s.vdim if s.out_gate else 0
+        self.proj_cols = self.q_cols + self.k_cols + self.v_cols + self.g_cols
+        if qkvg.out_features != self.proj_cols:
+            raise ValueError(f"layer {layer}: fused projection has {qkvg.out_features} rows, the mixer needs {self.proj_cols}")
+        sl = spec.slopes()
+        self.slopes = from_numpy(np.asarray(sl, np.float32)) if sl else None
+        self.queries_per_tile = int(api.seq_queries_per_tile(s.heads, s.kv_heads))
+
+    @property
+    def weight_bytes(self) -> int:
+        return self.qkvg.nbytes + self.o_proj.nbytes
+
+    def forward(self, ctx, x: GPUArray, out: GPUArray) -> None:
+        """x [T, W] -> out [T, W] (the mixer's output before the block's norm); K / V of the T tokens enter the cache."""
+        s, T = self.spec, ctx.T
+        W = self.qkvg.in_features
+        proj, attn = ctx.buf.proj, ctx.buf.attn
+        ld = self.proj_cols
+        self.qkvg.forward(x.device_ptr, W, T, proj.device_ptr, ld)
+        cache = ctx.cache
+        kc, vc = cache.k[self.layer], cache.v[self.layer]
+        api.seq_mixer_prep(proj.device_ptr, ld, T, s.heads, s.kv_heads, s.dim, s.vdim, self.q_norm.device_ptr,
+                           self.k_norm.device_ptr, self.eps, self.v_role, self.v_lambda,
+                           ctx.buf.v_first.device_ptr if self.v_role else None, kc.device_ptr, vc.device_ptr,
+                           cache.dtype_code, cache.table_dev.device_ptr, cache.pool.max_pages, cache.page_size,
+                           ctx.slot_ptr, ctx.pos_ptr, _st())
+        tiles_ptr, n_tiles = ctx.tiles(self.queries_per_tile)
+        ldo = s.heads * s.vdim
+        api.seq_attention(proj.device_ptr, ld, 0, self.q_cols + self.k_cols + self.v_cols, attn.device_ptr, ldo,
+                          kc.device_ptr, vc.device_ptr, cache.dtype_code, cache.table_dev.device_ptr, cache.pool.max_pages,
+                          cache.page_size, tiles_ptr, n_tiles, self.slopes.device_ptr if self.slopes is not None else None,
+                          s.heads, s.kv_heads, s.dim, s.vdim, s.chunk, s.scale, s.softcap, 1 if s.out_gate else 0, _st())
+        self.o_proj.forward(attn.device_ptr, ldo, T, out.device_ptr, self.o_proj.out_features)
+
+
+__all__ = ["PagedAttentionMixer"]

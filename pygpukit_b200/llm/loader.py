@@ -26,7 +26,7 @@ import numpy as np
 from ..core.array import GPUArray
 from ..core.dtypes import bfloat16, f32_to_bf16_bits, uint8
 from ..core.factory import from_numpy
-from .config import (GPT2_SPEC, MODEL_SPECS, ModelSpec, TransformerConfig, detect_model_spec)
+from .config import (GPT2_SPEC, LAYERED_ARCHITECTURES, MODEL_SPECS, ModelSpec, TransformerConfig, detect_model_spec)
 from .layers.attention import Attention
 from .layers.block import TransformerBlock
 from .layers.linear import LinearBF16, LinearFP8, LinearNVF4
@@ -119,6 +119,15 @@ def load_model_from_safetensors(model_path: str, dtype: str = "bfloat16", spec: 
                                 repack_weights: bool = True, weight_format: str | None = None,
                                 max_position_embeddings: int | None = None, config: dict | None = None) -> CausalTransformerModel:
     """See the module docstring.  dtype must be "bfloat16" (the B200 decode path); `config` overrides config.json."""
+    # layered families (config.json "architecture", llm/config.py LAYERED_ARCHITECTURES) have their own builder
+    lc = dict(config or {})
+    lc_path = os.path.join(model_path if os.path.isdir(model_path) else os.path.dirname(os.path.abspath(model_path)), "config.json")
+    if not lc and os.path.exists(lc_path):
+        with open(lc_path, encoding="utf-8") as f:
+            lc = json.load(f)
+    if str(lc.get("architecture", "")).lower() in LAYERED_ARCHITECTURES:
+        from .loader_layered import load_layered_model
+        return load_layered_model(model_path, dtype, lc)
     if dtype != "bfloat16":
         raise ValueError("the B200 decode path loads checkpoints as bfloat16 (FP8 weights stay FP8)")
     st = load_safetensors(model_path)

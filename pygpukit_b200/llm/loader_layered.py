@@ -1,0 +1,127 @@
+"""Checkpoint loading for the layered models (net-new; `loader.py` covers the uniform Hugging Face families).
+
+`load_layered_model(path, dtype)` reads `config.json` (its "architecture" picks the family, llm/config.py) and
+`model.safetensors` next to it; `build_layered_model(config, tensors, dtype)` takes the tensors as a
+{name: float32 ndarray} dictionary (tests, random initialisation).  dtype "bfloat16": matrices go to the device as
+bfloat16 (rounded to nearest even when the file holds wider floats), cache in bfloat16; "float32": matrices and
+cache in float32.  Norm weights, biases and other small vectors are float32 on the device in both modes.
+
+Dolurax tensor names: embed, head, final.norm(.b); per layer l<i>.norm1(.b), l<i>.norm2(.b), l<i>.mix.{q,k,v,g,o},
+l<i>.mix.{q,k}.norm, l<i>.mix.vmix (scalar), l<i>.mlp.router, l<i>.mlp.e<j>.{gate,up,down},
+l<i>.mlp.shared.{gate,up,down}; linear weights [out, in].  q, k, v and the gate are fused row-wise into one
+projection, gate/up pairs are interleaved row by row for the SiLU-multiply epilogue, experts are stacked.
+"""
+from __future__ import annotations
+
+import json
+import os
+
+import numpy as np
+
+from ..core.array import GPUArray
+from ..core.dtypes import bf16_bits_to_f32, f32_to_bf16_bits
+from ..core.factory import from_numpy
+from .config import LayeredConfig, layered_config_from_json
+from .layers.block import PostNormBlock
+from .layers.linear import LinearRows, interleave_gate_up
+from .layers.moe_rows import GroupedRouterMoE
+from .layers.paged_attention import PagedAttentionMixer
+from .models.layered import LayeredCausalModel
+from .safetensors import load_safetensors
+
+
+class _Tensors:
+    """name -> float32 ndarray, from a dictionary or a safetensors file."""
+
+    def __init__(self, src):
+        self.src = src
+        self.is_file = not isinstance(src, dict)
+
+    def has(self, name: str) -> bool:
+        return name in self.src
+
+    def f32(self, name: str, shape: tuple | None = None) -> np.ndarray:
+        if not self.has(name):
+            raise KeyError(f"checkpoint has no tensor {name!r}")
+        if self.is_file:
+            info = self.src.tensor_info(name)
+            a = self.src.tensor(name)
+            a = bf16_bits_to_f32(a).reshape(info.shape) if info.dtype == "BF16" else np.asarray(a, np.float32).reshape(info.shape)
+        else:
+            a = np.asarray(self.src[name], np.float32)
+        if shape is not None and tuple(a.shape) != tuple(shape):
+            raise ValueError(f"tensor {name!r} has shape {tuple(a.shape)}, the config needs {tuple(shape)}")
+        return a
+
+
+def _matrix(a: np.ndarray, dtype: str) -> GPUArray:
+    a = np.ascontiguousarray(a, np.float32)
+    return from_numpy(f32_to_bf16_bits(a).reshape(a.shape) if dtype == "bfloat16" else a)
+
+
+def _vector(a: np.ndarray) -> GPUArray:
+    return from_numpy(np.ascontiguousarray(a, np.float32))
+
+
+def build_layered_model(config: LayeredConfig, tensors, dtype: str = "bfloat16") -> LayeredCausalModel:
+    if dtype not in ("bfloat16", "float32"):
+        raise ValueError("layered models run in 'bfloat16' or 'float32'")
+    t = tensors if isinstance(tensors, _Tensors) else _Tensors(tensors)
+    W, V, eps = config.hidden_size, config.vocab_size, config.norm_eps
+    blocks = []
+    first_mix = None          # index and value width of the first value-mixing layer
+    for i, L in enumerate(config.layers):
+        p, m = f"l{i}.", L.mixer
+        mp = p + "mix."
+        parts = [t.f32(mp + "q", (m.heads * m.dim, W)), t.f32(mp + "k", (m.kv_heads * m.dim, W)),
+                 t.f32(mp + "v", (m.kv_heads * m.vdim, W))]
+        if m.out_gate:
+            parts.append(t.f32(mp + "g", (m.heads * m.vdim, W)))
+        qkvg = LinearRows(_matrix(np.concatenate(parts), dtype))
+        o_proj = LinearRows(_matrix(t.f32(mp + "o", (W, m.heads * m.vdim)), dtype))
+        role, lam = 0, 0.0
+        if m.v_mix:
+            if first_mix is None:
+                first_mix, role = (i, m.kv_heads * m.vdim), 1
+            else:
+                if m.kv_heads * m.vdim != first_mix[1]:
+                    raise ValueError(f"layer {i} mixes values of width {m.kv_heads * m.vdim} with layer {first_mix[0]}'s {first_mix[1]}")
+                role, lam = 2, float(t.f32(mp + "vmix").reshape(-1)[0])
+        mixer = PagedAttentionMixer(m, i, qkvg, o_proj, _vector(t.f32(mp + "q.norm", (m.dim,))),
+                                    _vector(t.f32(mp + "k.norm", (m.dim,))), eps, role, lam)
+        norm1 = (_vector(t.f32(p + "norm1", (W,))), _vector(t.f32(p + "norm1.b", (W,))))
+        mlp = norm2 = None
+        if L.mlp is not None:
+            f, q = L.mlp, p + "mlp."
+            gu = np.stack([interleave_gate_up(t.f32(f"{q}e{e}.gate", (f.ff, W)), t.f32(f"{q}e{e}.up", (f.ff, W)))
+                           for e in range(f.experts)])
+            dn = np.stack([t.f32(f"{q}e{e}.down", (W, f.ff)) for e in range(f.experts)])
+            sgu = sdn = None
+            if f.shared_ff:
+                s = q + "shared."
+                sgu = LinearRows(_matrix(interleave_gate_up(t.f32(s + "gate", (f.shared_ff, W)), t.f32(s + "up", (f.shared_ff, W))),
+                                         dtype), epilogue=1)
+                sdn = LinearRows(_matrix(t.f32(s + "down", (W, f.shared_ff)), dtype))
+            mlp = GroupedRouterMoE(f, _matrix(t.f32(q + "router", (f.experts, W)), dtype),
+                                   LinearRows(_matrix(gu, dtype), epilogue=1), LinearRows(_matrix(dn, dtype)), sgu, sdn)
+            norm2 = (_vector(t.f32(p + "norm2", (W,))), _vector(t.f32(p + "norm2.b", (W,))))
+        blocks.append(PostNormBlock(mixer, norm1, mlp, norm2, eps))
+    head = LinearRows(_matrix(t.f32("head", (V, W)), dtype), epilogue=2, scale=config.logit_scale, cap=config.logit_softcap)
+    final = (_vector(t.f32("final.norm", (W,))), _vector(t.f32("final.norm.b", (W,))))
+    return LayeredCausalModel(config, _matrix(t.f32("embed", (V, W)), dtype), blocks, final, head, dtype)
+
+
+def load_layered_model(model_path: str, dtype: str = "bfloat16", config: dict | None = None) -> LayeredCausalModel:
+    """`model_path`: a folder holding config.json + model.safetensors, or the safetensors file itself."""
+    folder = model_path if os.path.isdir(model_path) else os.path.dirname(os.path.abspath(model_path))
+    st_path = os.path.join(folder, "model.safetensors") if os.path.isdir(model_path) else model_path
+    if config is None:
+        with open(os.path.join(folder, "config.json"), encoding="utf-8") as f:
+            config = json.load(f)
+    cfg = layered_config_from_json(config)
+    if cfg is None:
+        raise ValueError(f"config.json names no layered architecture (got {config.get('architecture')!r})")
+    return build_layered_model(cfg, _Tensors(load_safetensors(st_path)), dtype)
+
+
+__all__ = ["build_layered_model", "load_layered_model"]

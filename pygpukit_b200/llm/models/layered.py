@@ -1,0 +1,190 @@
+"""LayeredCausalModel: decoder-only models described layer by layer (`LayeredConfig`), served token-major on the
+paged cache (net-new; the reference's `CausalTransformerModel`, models/causal.py:78-1493, runs uniform stacks, one
+sequence at a time, in 16 bits).
+
+One step = one ragged batch: for every request its next tokens (a whole prompt, a portion of one, or one decoded
+token), concatenated into T rows.  The residual stream, the norms, softmax, the router and every other
+non-matrix-product step are float32; matrix products take bfloat16 weights with float32 accumulation (dtype
+"bfloat16", the serving mode, cache in bfloat16) or float32 weights and cache (dtype "float32").  The logits of a
+position depend only on the sequence's own tokens: rows of different requests meet in no reduction.
+
+    model.step([(id, tokens, want), ...], end=[ids]) -> float32 logits [sum(len(want)), vocab] on the host
+    model.generate(prompts, max_new_tokens, temperature, ...) -> list of token lists (llm/decode/ragged.py)
+
+The step function is the only forward pass; `generate`, the scheduler and bin/trace_run all go through it.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from ..._lib import api
+from ...core.array import GPUArray
+from ...core.dtypes import float32, int32
+from ...core.stream import current_stream_handle as _st
+from ..buffers import RowBuffers
+from ..config import LayeredConfig
+from ..layers.block import PostNormBlock
+from ..layers.linear import LinearRows
+from ..paged_cache import PagedKVCache
+
+
+class StepContext:
+    """Device-side description of one ragged batch (one int32 upload per step)."""
+
+    def __init__(self, model: "LayeredCausalModel", entries, tile_sizes: set[int], tops: set[int]):
+        cache = model.cache
+        toks, slots, poss, want_rows, seqs = [], [], [], [], []
+        row = 0
+        for seq_id, tokens, want in entries:
+            n = len(tokens)
+            if n < 1:
+                raise ValueError(f"request {seq_id!r}: a step needs at least one token")
+            slot, pos0 = cache.extend(seq_id, n)
+            toks.extend(int(t) for t in tokens)
+            slots.extend([slot] * n)
+            poss.extend(range(pos0, pos0 + n))
+            for w in want:
+                if not 0 <= int(w) < n:
+                    raise ValueError(f"request {seq_id!r}: wanted place {w} outside its {n} tokens")
+                want_rows.append(row + int(w))
+            seqs.append((row, n, slot, pos0))
+            row += n
+        self.T, self.n_want = row, len(want_rows)
+        parts = [np.asarray(toks, np.int32), np.asarray(slots, np.int32), np.asarray(poss, np.int32),
+                 np.asarray(want_rows, np.int32)]
+        off = {"tok": 0, "slot": self.T, "pos": 2 * self.T, "want": 3 * self.T}
+        cur = 3 * self.T + self.n_want
+        self._rows_off = {}
+        if self.T <= LinearRows.FEW:
+            for top in sorted(tops):
+                n = self.T * top
+                parts += [np.repeat(np.arange(self.T, dtype=np.int32), top), np.arange(n, dtype=np.int32)]
+                self._rows_off[top] = (cur, cur + n)
+                cur += 2 * n
+        self._tiles_off = {}
+        for qt in sorted(tile_sizes):
+            pad = (-cur) % 4                       # int4 loads: 16-byte aligned
+            if pad:
+                parts.append(np.zeros(pad, np.int32))
+                cur += pad
+            t = [(r0 + i, min(qt, n - i), slot, p0 + i) for r0, n, slot, p0 in seqs for i in range(0, n, qt)]
+            parts.append(np.asarray(t, np.int32).reshape(-1))
+            self._tiles_off[qt] = (cur, len(t))
+            cur += 4 * len(t)
+        meta = np.concatenate(parts)
+        self.meta = model._meta_buffer(meta.size)
+        api.memcpy_h2d(self.meta.device_ptr, meta.ctypes.data, meta.nbytes, _st())
+        api.stream_sync(_st()) if _st() is not None else api.device_sync()
+        base = self.meta.device_ptr
+        self.tok_ptr, self.slot_ptr, self.pos_ptr, self.want_ptr = (base + 4 * off[k] for k in ("tok", "slot", "pos", "want"))
+        self._base = base
+        cache.sync_table()
+        self.cache = cache
+        self.buf = model._buffers(self.T)
+
+    def tiles(self, queries_per_tile: int) -> tuple[int, int]:
+        off, n = self._tiles_off[queries_per_tile]
+        return self._base + 4 * off, n
+
+    def slot_rows(self, top: int) -> tuple[int, int]:
+        """(token of every (token, slot) row, 0 .. T * top - 1) for the few-row expert path"""
+        a, b = self._rows_off[top]
+        return self._base + 4 * a, self._base + 4 * b
+
+
+class LayeredCausalModel:
+    def __init__(self, config: LayeredConfig, embed_tokens: GPUArray, blocks: list[PostNormBlock],
+                 final_norm: tuple[GPUArray, GPUArray], lm_head: LinearRows, dtype: str = "bfloat16"):
+        self.config, self.embed_tokens, self.blocks = config, embed_tokens, blocks
+        self.final_norm, self.lm_head, self.dtype = final_norm, lm_head, dtype
+        self.embed_dt = 2 if embed_tokens.dtype.name == "bfloat16" else 0
+        self.cache: PagedKVCache | None = None
+        self._buf: RowBuffers | None = None
+        self._meta: GPUArray | None = None
+        self._out: GPUArray | None = None
+        self._tile_sizes = {b.mixer.queries_per_tile for b in blocks}
+        self._tops = {b.mlp.spec.top for b in blocks if b.mlp is not None}
+
+    # ------------------------------------------------------------------ setup
+    def init_cache(self, max_tokens: int = 4096, page_size: int = 64, slots: int = 8) -> PagedKVCache:
+        """Allocate the paged cache for about `max_tokens` live positions (it grows when more arrive)."""
+        shapes = [(b.mixer.spec.kv_heads, b.mixer.spec.dim, b.mixer.spec.vdim) for b in self.blocks]
+        self.cache = PagedKVCache(shapes, self.dtype, page_size, max_tokens, slots)
+        return self.cache
+
+    def _buffers(self, rows: int) -> RowBuffers:
+        if self._buf is None or self._buf.rows < rows:
+            self._buf = RowBuffers(self.config, max(rows, 2 * self._buf.rows if self._buf else 0))
+        return self._buf
+
+    def _meta_buffer(self, n: int) -> GPUArray:
+        if self._meta is None or self._meta.size < n:
+            self._meta = GPUArray((max(1024, 2 * n),), int32)
+        return self._meta
+
+    # ------------------------------------------------------------------ the step
+    def step_device(self, entries, end=()) -> tuple[GPUArray | None, int]:
+        """Run one ragged batch; returns (float32 logits [n_want, vocab] on the device or None, n_want).  `end` names
+        the requests whose cache is given back after the step."""
+        if self.cache is None:
+            self.init_cache()
+        cfg = self.config
+        W, V = cfg.hidden_size, cfg.vocab_size
+        ctx = StepContext(self, entries, self._tile_sizes, self._tops)
+        b, T = ctx.buf, ctx.T
+        x = b.x
+        api.embed_rows_f32(self.embed_tokens.device_ptr, self.embed_dt, ctx.tok_ptr, x.device_ptr, T, W, V, _st())
+        for blk in self.blocks:
+            blk.forward(ctx, x)
+        out = None
+        if ctx.n_want:
+            n = ctx.n_want
+            if self._out is None or self._out.shape[0] < n:
+                self._out = GPUArray((max(n, 16), V), float32)
+            xn = b.y                                   # free after the last block
+            api.combine_layernorm_f32(x.device_ptr, ctx.want_ptr, None, None, None, 0, self.final_norm[0].device_ptr,
+                                      self.final_norm[1].device_ptr, cfg.norm_eps, xn.device_ptr, n, W, 0, _st())
+            self.lm_head.forward(xn.device_ptr, W, n, self._out.device_ptr, V)
+            out = self._out
+        for seq_id in end:
+            self.cache.release(seq_id)
+        return out, ctx.n_want
+
+    def step(self, entries, end=()) -> np.ndarray:
+        """`step_device` with the wanted logits copied to the host ([n_want, vocab] float32)."""
+        out, n = self.step_device(entries, end)
+        V = self.config.vocab_size
+        if not n:
+            api.stream_sync(_st()) if _st() is not None else api.device_sync()
+            return np.zeros((0, V), np.float32)
+        host = np.empty((n, V), np.float32)
+        api.memcpy_d2h(host.ctypes.data, out.device_ptr, host.nbytes, _st())
+        api.stream_sync(_st()) if _st() is not None else api.device_sync()
+        return host
+
+    def release(self, seq_id) -> None:
+        self.cache.release(seq_id)
+
+    def residual_rows(self, n: int) -> np.ndarray:
+        """The first n rows of the residual stream as the last step left them (debugging aid)."""
+        return self._buf.x.to_numpy()[:n].copy()
+
+    # ------------------------------------------------------------------ generation
+    def generate(self, prompts, max_new_tokens: int = 20, temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0,
+                 eos_token_id: int | None = None, prefill_chunk: int | None = None) -> list[list[int]]:
+        """Generate for one prompt (a list of ints) or several (a list of lists) through the batch scheduler."""
+        from ..decode.ragged import RaggedScheduler
+        single = bool(prompts) and isinstance(prompts[0], (int, np.integer))
+        sched = RaggedScheduler(self, prefill_chunk=prefill_chunk)
+        for i, p in enumerate([prompts] if single else prompts):
+            sched.add_request(i, list(p), max_new_tokens, temperature, top_k, top_p, eos_token_id)
+        done = sched.run()
+        outs = [done[i] for i in range(len(done))]
+        return outs[0] if single else outs
+
+    # ------------------------------------------------------------------ accounting
+    def weight_bytes_per_token(self) -> int:
+        return sum(b.weight_bytes for b in self.blocks) + self.lm_head.nbytes
+
+
+__all__ = ["LayeredCausalModel", "StepContext"]
