@@ -8,7 +8,7 @@ from .config import (GPT2_SPEC, LLAMA_SPEC, MIXTRAL_SPEC, MODEL_SPECS, QWEN2_SPE
                      named_config, AttentionMixerSpec, LayeredConfig, LayerSpec, MoESpec, layered_config_from_json)
 from .decode import (DecodeBatch, DecodeJacobi, DecodeM1, DecodeM1Graph, DecodeSpeculative, DecodeStrategy,
                      RaggedScheduler)
-from .layers import (MLP, Attention, GroupedRouterMoE, Linear, LinearBF16, LinearFP8, LinearNVF4, LinearRows, MoELayer, Norm,
+from .layers import (MLP, Attention, GroupedRouterMoE, Linear, LinearBF16, LinearFP8, LinearNVF4, LinearRows, MoELayer, Norm, interleave_gate_up,
                      PagedAttentionMixer, PostNormBlock, TransformerBlock,
                      apply_rotary_pos_emb_numpy, precompute_freqs_cis)
 from .models import CausalTransformerModel, GPT2Model, LayeredCausalModel, LlamaModel, QwenModel
