@@ -74,6 +74,10 @@ def parse_args():
     ap.add_argument("--configs", default="all", help="'all' (default), 'none', or a comma list of sub-config keys")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=None, help="debug: truncate the model (INVALID as a bench number)")
+    ap.add_argument("--layered", action="store_true",
+                    help="instead of the default workload: prefill / decode throughput of the layered (Dolurax) family at "
+                         "real layer sizes beside Qwen3-MoE at equal sizes (scripts/bench_layered.py), one JSON line")
+    ap.add_argument("--layered-sizes", default="a3b-2048,moe-4096")
     return ap.parse_args()
 
 
@@ -599,6 +603,11 @@ def run_ours(args) -> None:
 
 def main():
     args = parse_args()
+    if args.layered:
+        sys.path.insert(0, os.path.join(ROOT, "scripts"))
+        import bench_layered
+        print(json.dumps(bench_layered.main(ROOT, args.layered_sizes.split(","), args.steps, args.warmup)))
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -491,13 +491,12 @@ int pgk_embed_rows_f32(const void* table, int wdt, const int32_t* tokens, float*
 int pgk_combine_layernorm_f32(const float* base, const int32_t* src_rows, const float* parts, const int32_t* inv,
                               const float* weights, int top, const float* gamma, const float* beta, float eps, float* out,
                               int rows, int width, int add, void* stream);
-/* router: scores = softmax(x . router^T) over all experts; with group_count > 1 only members of the group_keep groups of
- * neighbours with the largest member score may be chosen; the `top` largest (ties: lowest index) -> idx [tokens, top],
- * weights = chosen scores / (their sum + 1e-20).  counts (zeroed, or NULL) receives the rows per expert and rank the
- * arrival number of every (token, slot) at its expert. */
-int pgk_moe_route_grouped(const float* x, int ldx, const void* router, int wdt, int tokens, int width, int experts, int top,
-                          int group_count, int group_keep, int32_t* idx, float* weights, int32_t* rank, int32_t* counts,
-                          void* stream);
+/* router selection on the logits [tokens, experts] (row stride ld) of the router GEMM: scores = softmax over all experts;
+ * with group_count > 1 only members of the group_keep groups of neighbours with the largest member score may be chosen;
+ * the `top` largest (ties: lowest index) -> idx [tokens, top], weights = chosen scores / (their sum + 1e-20).  counts
+ * (zeroed, or NULL) receives the rows per expert and rank the arrival number of every (token, slot) at its expert. */
+int pgk_moe_route_grouped(const float* logits, int ld, int tokens, int experts, int top, int group_count, int group_keep,
+                          int32_t* idx, float* weights, int32_t* rank, int32_t* counts, void* stream);
 /* offsets [experts + 1] = exclusive scan of counts (cleared afterwards); perm[row] = token of the row, inv[t * top + k] = row */
 int pgk_moe_row_lists(int32_t* counts, int32_t* offsets, const int32_t* idx, const int32_t* rank, int32_t* perm, int32_t* inv,
                       int experts, int tokens, int top, void* stream);
@@ -512,11 +511,13 @@ int pgk_seq_mixer_prep(float* proj, int ld, int tokens, int heads, int kv_heads,
 /* tiles [n_tiles][4] = (first row, queries <= pgk_seq_queries_per_tile, slot, first position): consecutive positions of one
  * sequence.  score = scale q.k, cap * tanh(score / cap) when cap > 0, minus slopes[h] * (i - j) when slopes; key j visible
  * from i when j <= i and (chunk > 0) floor(j / chunk) == floor(i / chunk); out [row, heads x vdim], times
- * sigmoid(proj[row, gate_off + ...]) when gate != 0. */
+ * sigmoid(proj[row, gate_off + ...]) when gate != 0.  splits > 1 (few long tiles: decoding) cuts every tile's key range
+ * into that many slices over grid.z; their partial (max, sum, P.V) records go through workspace
+ * [rows][heads][splits][vdim + 2] and a second launch folds them. */
 int pgk_seq_attention(const float* proj, int ld, int q_off, int gate_off, float* out, int ldo, const void* k_cache,
                       const void* v_cache, int cache_dtype, const int32_t* table, int max_pages, int page_size,
                       const int32_t* tiles, int n_tiles, const float* slopes, int heads, int kv_heads, int dim, int vdim,
-                      int chunk, float scale, float softcap, int gate, void* stream);
+                      int chunk, float scale, float softcap, int gate, int splits, float* workspace, int rows, void* stream);
 int pgk_seq_heads_per_block(int heads, int kv_heads);
 int pgk_seq_queries_per_tile(int heads, int kv_heads);
 

@@ -34,14 +34,16 @@ struct PrepArgs {
     const int* slot; const int* pos;
 };
 
+// units: H query heads, G key heads, G value heads; one warp each, four per block
 template <typename TC>
 __global__ void __launch_bounds__(128) mixer_prep_kernel(PrepArgs a) {
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int u = blockIdx.y * 4 + warp;
+    if (u >= a.H + 2 * a.G) return;
     float* row = a.proj + (size_t)t * a.ld;
     const int pos = a.pos[t], slot = a.slot[t];
     const int page = a.table[(size_t)slot * a.max_pages + pos / a.PS], r = pos % a.PS;
-    const int koff = a.H * a.D, voff = koff + a.G * a.D;
-    for (int u = warp; u < a.H + a.G; u += 4) {
+    if (u < a.H + a.G) {
         float* x = row + (size_t)u * a.D;            // query heads then key heads are contiguous
         float ss = 0.f;
         for (int d = lane; d < a.D; d += 32) ss = fmaf(x[d], x[d], ss);
@@ -54,14 +56,16 @@ __global__ void __launch_bounds__(128) mixer_prep_kernel(PrepArgs a) {
             TC* dst = (TC*)a.kc + (((size_t)page * a.G + g) * a.PS + r) * a.D;
             for (int d = lane; d < a.D; d += 32) cstore<TC>(dst + d, x[d] * inv * a.kw[d]);
         }
+        return;
     }
-    const int GV = a.G * a.Dv;
-    for (int i = threadIdx.x; i < GV; i += blockDim.x) {
-        float v = row[voff + i];
-        if (a.vmode == 1) a.vfirst[(size_t)t * GV + i] = v;
-        else if (a.vmode == 2) v = (1.f - a.lam) * v + a.lam * a.vfirst[(size_t)t * GV + i];
-        const int g = i / a.Dv, d = i - g * a.Dv;
-        cstore<TC>((TC*)a.vc + (((size_t)page * a.G + g) * a.PS + r) * a.Dv + d, v);
+    const int g = u - a.H - a.G, GV = a.G * a.Dv;
+    const int voff = a.H * a.D + a.G * a.D + g * a.Dv;
+    TC* dst = (TC*)a.vc + (((size_t)page * a.G + g) * a.PS + r) * a.Dv;
+    for (int d = lane; d < a.Dv; d += 32) {
+        float v = row[voff + d];
+        if (a.vmode == 1) a.vfirst[(size_t)t * GV + g * a.Dv + d] = v;
+        else if (a.vmode == 2) v = (1.f - a.lam) * v + a.lam * a.vfirst[(size_t)t * GV + g * a.Dv + d];
+        cstore<TC>(dst + d, v);
     }
 }
 
@@ -73,9 +77,40 @@ struct AttnArgs {
     const float* slopes;                // [H] or NULL
     int H, G, D, Dv, chunk, HB, gate;
     float scale, cap;
+    int splits; float* ws;              // splits > 1: partial (m, l, acc[Dv]) records [row][H][splits][Dv + 2]
 };
 
 constexpr int KT = 32;                  // keys per tile = one per lane
+
+// KT cache rows of n elements -> shared memory as float32 (row stride ld), 16 bytes per load when the rows allow it;
+// rows with offset < 0 (past the last key) are zero-filled
+template <typename TC>
+__device__ __forceinline__ void stage_rows(float* dst, int ld, const TC* base, const long long* row_off, int n) {
+    constexpr int VEC = 16 / sizeof(TC);
+    if (n % VEC == 0) {
+        const int vpr = n / VEC;
+        for (int i = threadIdx.x; i < KT * vpr; i += blockDim.x) {
+            const int r = i / vpr, c = (i - r * vpr) * VEC;
+            float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (row_off[r] >= 0) {
+                const uint4 v = *(const uint4*)(base + row_off[r] + c);
+                if (sizeof(TC) == 2) {
+                    f[0] = bf16lo(v.x); f[1] = bf16hi(v.x); f[2] = bf16lo(v.y); f[3] = bf16hi(v.y);
+                    f[4] = bf16lo(v.z); f[5] = bf16hi(v.z); f[6] = bf16lo(v.w); f[7] = bf16hi(v.w);
+                } else {
+                    f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < VEC; ++q) dst[r * ld + c + q] = f[q];
+        }
+        return;
+    }
+    for (int i = threadIdx.x; i < KT * n; i += blockDim.x) {
+        const int r = i / n, d = i - r * n;
+        dst[r * ld + d] = row_off[r] >= 0 ? cload<TC>(base + row_off[r] + d) : 0.f;
+    }
+}
 constexpr int PPW = 4;                  // (query, head) pairs per warp
 constexpr int NWARP = 8;
 
@@ -110,6 +145,7 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
         lo[c] = a.chunk > 0 ? (pi[c] / a.chunk) * a.chunk : 0;
         slope[c] = (ok[c] && a.slopes) ? a.slopes[hd[c]] : 0.f;
     }
+    const bool warp_live = ok[0] || ok[1] || ok[2] || ok[3];
     for (int i = lane; i < D * PPW; i += 32) {
         const int d = i / PPW, c = i - d * PPW;
         float v = 0.f;
@@ -128,7 +164,11 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
     const int jlo = a.chunk > 0 ? (pos0 / a.chunk) * a.chunk : 0, jhi = pos0 + nq - 1;
     const TC* kc = (const TC*)a.kc;
     const TC* vc = (const TC*)a.vc;
-    for (int j0 = jlo; j0 <= jhi; j0 += KT) {
+    // this block's slice of the key tiles (all of them when splits == 1)
+    const int ntile = (jhi - jlo) / KT + 1, per = (ntile + a.splits - 1) / a.splits;
+    const int jbeg = jlo + (int)blockIdx.z * per * KT;
+    const int jend = min(jhi, jbeg + per * KT - 1);
+    for (int j0 = jbeg; j0 <= jend; j0 += KT) {
         __syncthreads();
         if (threadIdx.x < KT) {
             const int j = j0 + threadIdx.x;
@@ -141,15 +181,10 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
             krow[threadIdx.x] = ko; vrow[threadIdx.x] = vo;
         }
         __syncthreads();
-        for (int i = threadIdx.x; i < KT * D; i += blockDim.x) {
-            const int r = i / D, d = i - r * D;
-            Ks[r * DP + d] = krow[r] >= 0 ? cload<TC>(kc + krow[r] + d) : 0.f;
-        }
-        for (int i = threadIdx.x; i < KT * Dv; i += blockDim.x) {
-            const int r = i / Dv, d = i - r * Dv;
-            Vs[i] = vrow[r] >= 0 ? cload<TC>(vc + vrow[r] + d) : 0.f;
-        }
+        stage_rows<TC>(Ks, DP, kc, krow, D);
+        stage_rows<TC>(Vs, Dv, vc, vrow, Dv);
         __syncthreads();
+        if (!warp_live) continue;                   // a warp without a (query, head) pair only helps staging
         // scores: lane = key
         float s[PPW] = {};
         const float* kr = Ks + lane * DP;
@@ -192,6 +227,18 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
             }
         }
     }
+    if (a.splits > 1) {
+#pragma unroll
+        for (int c = 0; c < PPW; ++c) {
+            if (!ok[c]) continue;
+            float* rec = a.ws + (((size_t)(t0 + qi[c]) * a.H + hd[c]) * a.splits + blockIdx.z) * (Dv + 2);
+            if (lane == 0) { rec[0] = m[c]; rec[1] = l[c]; }
+#pragma unroll
+            for (int v = 0; v < NV; ++v)
+                if (lane + 32 * v < Dv) rec[2 + lane + 32 * v] = acc[c][v];
+        }
+        return;
+    }
 #pragma unroll
     for (int c = 0; c < PPW; ++c) {
         if (!ok[c]) continue;
@@ -211,6 +258,37 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
     }
 }
 
+// fold the partial records of the key slices: one warp per (row, head)
+__global__ void __launch_bounds__(128) seq_attention_merge_kernel(AttnArgs a, int rows) {
+    const int lane = threadIdx.x & 31, w = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (w >= rows * a.H) return;
+    const int t = w / a.H, h = w - t * a.H, Dv = a.Dv;
+    const float* rec = a.ws + (size_t)w * a.splits * (Dv + 2);
+    float M = -INFINITY;
+    for (int s = lane; s < a.splits; s += 32) M = fmaxf(M, rec[(size_t)s * (Dv + 2)]);
+    M = warp_max(M);
+    float L = 0.f;
+    for (int s = lane; s < a.splits; s += 32) {
+        const float ms = rec[(size_t)s * (Dv + 2)];
+        if (ms != -INFINITY) L += rec[(size_t)s * (Dv + 2) + 1] * expf(ms - M);
+    }
+    L = warp_sum(L);
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    for (int dv = lane; dv < Dv; dv += 32) {
+        float o = 0.f;
+        for (int s = 0; s < a.splits; ++s) {
+            const float ms = rec[(size_t)s * (Dv + 2)];
+            if (ms != -INFINITY) o = fmaf(rec[(size_t)s * (Dv + 2) + 2 + dv], expf(ms - M), o);
+        }
+        o *= inv;
+        if (a.gate) {
+            const float z = a.proj[(size_t)t * a.ld + a.g_off + (size_t)h * Dv + dv];
+            o *= 1.f / (1.f + expf(-z));
+        }
+        a.out[(size_t)t * a.ldo + (size_t)h * Dv + dv] = o;
+    }
+}
+
 template <typename TC, int NV>
 int launch_attn(const AttnArgs& a, int tiles, cudaStream_t st) {
     const size_t smem = sizeof(float) * ((size_t)NWARP * a.D * PPW + (size_t)KT * (a.D + 1) + (size_t)KT * a.Dv);
@@ -221,7 +299,7 @@ int launch_attn(const AttnArgs& a, int tiles, cudaStream_t st) {
         configured = 1;
     }
     const int rep = a.H / a.G, hsplit = (rep + a.HB - 1) / a.HB;
-    PGK_CUDA(launch(seq_attention_kernel<TC, NV>, dim3(tiles, a.G * hsplit), dim3(256), smem, st, a));
+    PGK_CUDA(launch(seq_attention_kernel<TC, NV>, dim3(tiles, a.G * hsplit, a.splits), dim3(256), smem, st, a));
     return 0;
 }
 
@@ -256,22 +334,26 @@ int pgk_seq_mixer_prep(float* proj, int ld, int tokens, int heads, int kv_heads,
     if (tokens <= 0) return 0;
     PrepArgs a{proj, ld, heads, kv_heads, dim, vdim, q_weight, k_weight, eps, v_mode, lam, v_first, k_cache, v_cache, table,
                max_pages, page_size, slot, pos};
-    if (cache_dtype == 2) PGK_CUDA(launch(mixer_prep_kernel<uint16_t>, dim3(tokens), dim3(128), 0, (cudaStream_t)stream, a));
-    else PGK_CUDA(launch(mixer_prep_kernel<float>, dim3(tokens), dim3(128), 0, (cudaStream_t)stream, a));
+    if (cache_dtype == 2) PGK_CUDA(launch(mixer_prep_kernel<uint16_t>, dim3(tokens, (heads + 2 * kv_heads + 3) / 4), dim3(128), 0, (cudaStream_t)stream, a));
+    else PGK_CUDA(launch(mixer_prep_kernel<float>, dim3(tokens, (heads + 2 * kv_heads + 3) / 4), dim3(128), 0, (cudaStream_t)stream, a));
     return 0;
 }
 
 int pgk_seq_attention(const float* proj, int ld, int q_off, int gate_off, float* out, int ldo, const void* k_cache,
                       const void* v_cache, int cache_dtype, const int32_t* table, int max_pages, int page_size,
                       const int32_t* tiles, int n_tiles, const float* slopes, int heads, int kv_heads, int dim, int vdim,
-                      int chunk, float scale, float softcap, int gate, void* stream) {
+                      int chunk, float scale, float softcap, int gate, int splits, float* workspace, int rows, void* stream) {
     PGK_REQUIRE(cache_dtype == 0 || cache_dtype == 2, "seq_attention failed: the cache is float32 (0) or bfloat16 (2), got %d", cache_dtype);
     PGK_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0, "seq_attention failed: invalid head layout");
+    PGK_REQUIRE(splits >= 1 && splits <= 64 && (splits == 1 || workspace), "seq_attention failed: 1..64 key slices, more than one needs the workspace");
     if (n_tiles <= 0) return 0;
     AttnArgs a{proj, ld, q_off, gate_off, out, ldo, k_cache, v_cache, table, max_pages, page_size, (const int4*)tiles, slopes,
-               heads, kv_heads, dim, vdim, chunk, pgk_seq_heads_per_block(heads, kv_heads), gate, scale, softcap};
-    if (cache_dtype == 2) return launch_attn_nv<uint16_t>(a, n_tiles, (cudaStream_t)stream);
-    return launch_attn_nv<float>(a, n_tiles, (cudaStream_t)stream);
+               heads, kv_heads, dim, vdim, chunk, pgk_seq_heads_per_block(heads, kv_heads), gate, scale, softcap, splits, workspace};
+    const int rc = cache_dtype == 2 ? launch_attn_nv<uint16_t>(a, n_tiles, (cudaStream_t)stream)
+                                    : launch_attn_nv<float>(a, n_tiles, (cudaStream_t)stream);
+    if (rc || splits == 1) return rc;
+    PGK_CUDA(launch(seq_attention_merge_kernel, dim3((rows * heads + 3) / 4), dim3(128), 0, (cudaStream_t)stream, a, rows));
+    return 0;
 }
 
 }  // extern "C"

@@ -229,7 +229,7 @@ __global__ void __launch_bounds__(128) gemm_rows_f32_kernel(GemmArgs a) {
 }
 
 // ---------------------------------------------------------------- few rows: one warp per output column (pair)
-// Block = 8 warps; the block's rows of A (<= RMAX, all using the same weight matrix) sit in shared memory as float32;
+// Block = 4 .. 16 warps; the block's rows of A (<= RMAX, all using the same weight matrix) sit in shared memory as float32;
 // a warp owns two consecutive output columns (a gate/up pair under EPI 1), reads their weight rows once with 128-bit
 // loads and forms the dot products of every row.  grid = (column pairs / 8, row blocks).
 constexpr int RMAX = 8;
@@ -237,8 +237,7 @@ constexpr int RMAX = 8;
 template <typename TW> struct WLoad;
 template <> struct WLoad<uint16_t> {
     static constexpr int VEC = 8;
-    static __device__ __forceinline__ void load(const uint16_t* p, float (&w)[8]) {
-        const uint4 v = ldg_stream(p);
+    static __device__ __forceinline__ void unpack(const uint4& v, float (&w)[8]) {
         w[0] = bf16lo(v.x); w[1] = bf16hi(v.x); w[2] = bf16lo(v.y); w[3] = bf16hi(v.y);
         w[4] = bf16lo(v.z); w[5] = bf16hi(v.z); w[6] = bf16lo(v.w); w[7] = bf16hi(v.w);
     }
@@ -246,52 +245,94 @@ template <> struct WLoad<uint16_t> {
 };
 template <> struct WLoad<float> {
     static constexpr int VEC = 4;
-    static __device__ __forceinline__ void load(const float* p, float (&w)[8]) {
-        const uint4 v = ldg_stream(p);
+    static __device__ __forceinline__ void unpack(const uint4& v, float (&w)[8]) {
         w[0] = __uint_as_float(v.x); w[1] = __uint_as_float(v.y); w[2] = __uint_as_float(v.z); w[3] = __uint_as_float(v.w);
         w[4] = w[5] = w[6] = w[7] = 0.f;
     }
     static __device__ __forceinline__ float one(const float* p) { return *p; }
 };
 
+constexpr int FEW_MAX_WARPS = 16;  // warps (= column pairs) per block: 4 .. 16, more when the staged rows take much shared memory
+constexpr int FEW_UN = 4;         // 128-bit loads per weight row in flight per lane
+
 template <typename TW, int EPI, bool ROUND>
-__global__ void __launch_bounds__(256) gemm_few_rows_kernel(GemmArgs a, int rows_per_block) {
+__global__ void __launch_bounds__(FEW_MAX_WARPS * 32) gemm_few_rows_kernel(GemmArgs a, int rows_per_block) {
     extern __shared__ __align__(16) float xs[];                 // [rows][K]
     const int r0 = blockIdx.y * rows_per_block;
     const int nr = min(rows_per_block, a.M - r0);
     const int grp = a.row_group ? a.row_group[r0] : 0;
     const TW* W = (const TW*)a.W + (size_t)grp * a.w_stride;
-    for (int i = threadIdx.x; i < nr * a.K; i += blockDim.x) {
-        const int r = i / a.K, k = i - r * a.K;
-        const int gr = a.a_rows ? a.a_rows[r0 + r] : r0 + r;
-        float v = a.A[(size_t)gr * a.lda + k];
-        xs[i] = ROUND ? round_bf16(v) : v;
+    constexpr int VEC = WLoad<TW>::VEC;
+    const bool vec = (a.K % VEC == 0) && (((uintptr_t)W & 15) == 0);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int c0 = (blockIdx.x * (blockDim.x >> 5) + warp) * 2;
+    const bool live = c0 < a.N;
+    const bool two = c0 + 1 < a.N;
+    const TW* w0 = W + (size_t)(live ? c0 : 0) * a.K;
+    const TW* w1 = W + (size_t)(two ? c0 + 1 : (live ? c0 : 0)) * a.K;
+    // the first weight loads do not depend on the activations: issue them before staging x
+    uint4 ru[FEW_UN], rv[FEW_UN];
+    const int kstep = 32 * VEC;
+    if (vec) {
+#pragma unroll
+        for (int j = 0; j < FEW_UN; ++j) {
+            const int k = lane * VEC + j * kstep;
+            ru[j] = rv[j] = make_uint4(0u, 0u, 0u, 0u);
+            if (live && k < a.K) { ru[j] = ldg_stream(w0 + k); rv[j] = ldg_stream(w1 + k); }
+        }
+    }
+    const bool xvec = (a.K % 4 == 0) && (a.lda % 4 == 0) && (((uintptr_t)a.A & 15) == 0);
+    if (xvec) {
+        const int k4 = a.K >> 2;
+        for (int i = threadIdx.x; i < nr * k4; i += blockDim.x) {
+            const int r = i / k4, k = (i - r * k4) * 4;
+            const int gr = a.a_rows ? a.a_rows[r0 + r] : r0 + r;
+            float4 v = *(const float4*)(a.A + (size_t)gr * a.lda + k);
+            if (ROUND) { v.x = round_bf16(v.x); v.y = round_bf16(v.y); v.z = round_bf16(v.z); v.w = round_bf16(v.w); }
+            *(float4*)(xs + r * a.K + k) = v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < nr * a.K; i += blockDim.x) {
+            const int r = i / a.K, k = i - r * a.K;
+            const int gr = a.a_rows ? a.a_rows[r0 + r] : r0 + r;
+            const float v = a.A[(size_t)gr * a.lda + k];
+            xs[i] = ROUND ? round_bf16(v) : v;
+        }
     }
     __syncthreads();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int c0 = (blockIdx.x * 8 + warp) * 2;
-    if (c0 >= a.N) return;
-    const bool two = c0 + 1 < a.N;
-    const TW* w0 = W + (size_t)c0 * a.K;
-    const TW* w1 = W + (size_t)(two ? c0 + 1 : c0) * a.K;
-    constexpr int VEC = WLoad<TW>::VEC;
+    if (!live) return;
     float acc0[RMAX] = {}, acc1[RMAX] = {};
-    const bool vec = (a.K % VEC == 0) && (((uintptr_t)W & 15) == 0);
     if (vec) {
-        for (int k = lane * VEC; k < a.K; k += 32 * VEC) {
-            float u[8], v[8];
-            WLoad<TW>::load(w0 + k, u);
-            WLoad<TW>::load(w1 + k, v);
+        for (int kb = 0; kb < a.K; kb += FEW_UN * kstep) {
+            uint4 cu[FEW_UN], cv[FEW_UN];
 #pragma unroll
-            for (int r = 0; r < RMAX; ++r) {
-                if (r < nr) {
-                    float x[8];
-                    *(float4*)&x[0] = *(const float4*)(xs + r * a.K + k);
-                    if (VEC == 8) *(float4*)&x[4] = *(const float4*)(xs + r * a.K + k + 4);
+            for (int j = 0; j < FEW_UN; ++j) { cu[j] = ru[j]; cv[j] = rv[j]; }
+            const int kn = kb + FEW_UN * kstep;
+            if (kn < a.K) {
 #pragma unroll
-                    for (int j = 0; j < VEC; ++j) {
-                        acc0[r] = fmaf(x[j], u[j], acc0[r]);
-                        acc1[r] = fmaf(x[j], v[j], acc1[r]);
+                for (int j = 0; j < FEW_UN; ++j) {
+                    const int k = kn + lane * VEC + j * kstep;
+                    if (k < a.K) { ru[j] = ldg_stream(w0 + k); rv[j] = ldg_stream(w1 + k); }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < FEW_UN; ++j) {
+                const int k = kb + lane * VEC + j * kstep;
+                if (k >= a.K) continue;
+                float u[8], v[8];
+                WLoad<TW>::unpack(cu[j], u);
+                WLoad<TW>::unpack(cv[j], v);
+#pragma unroll
+                for (int r = 0; r < RMAX; ++r) {
+                    if (r < nr) {
+                        float x[8];
+                        *(float4*)&x[0] = *(const float4*)(xs + r * a.K + k);
+                        if (VEC == 8) *(float4*)&x[4] = *(const float4*)(xs + r * a.K + k + 4);
+#pragma unroll
+                        for (int q = 0; q < VEC; ++q) {
+                            acc0[r] = fmaf(x[q], u[q], acc0[r]);
+                            acc1[r] = fmaf(x[q], v[q], acc1[r]);
+                        }
                     }
                 }
             }
@@ -332,8 +373,10 @@ int launch_few_t(const GemmArgs& a, int rows_per_block, cudaStream_t st) {
         PGK_CUDA(cudaFuncSetAttribute(gemm_few_rows_kernel<TW, EPI, ROUND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         configured = 200 * 1024;
     }
-    dim3 grid(((a.N + 1) / 2 + 7) / 8, (a.M + rows_per_block - 1) / rows_per_block);
-    PGK_CUDA(launch(gemm_few_rows_kernel<TW, EPI, ROUND>, grid, dim3(256), smem, st, a, rows_per_block));
+    // a block's shared memory decides how many blocks fit an SM: keep about 16 warps per SM streaming
+    const int warps = smem <= 48 * 1024 ? 4 : (smem <= 100 * 1024 ? 8 : FEW_MAX_WARPS);
+    dim3 grid(((a.N + 1) / 2 + warps - 1) / warps, (a.M + rows_per_block - 1) / rows_per_block);
+    PGK_CUDA(launch(gemm_few_rows_kernel<TW, EPI, ROUND>, grid, dim3(warps * 32), smem, st, a, rows_per_block));
     return 0;
 }
 

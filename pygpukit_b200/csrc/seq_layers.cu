@@ -14,12 +14,18 @@ template <> __device__ __forceinline__ float wload<float>(const float* p) { retu
 template <> __device__ __forceinline__ float wload<uint16_t>(const uint16_t* p) { return bf16_bits_to_f32(*p); }
 
 template <typename TW>
-__global__ void embed_rows_kernel(const TW* table, const int* tok, float* x, int W, int vocab) {
+__global__ void __launch_bounds__(256) embed_rows_kernel(const TW* table, const int* tok, float* x, int W, int vocab) {
     const int t = blockIdx.x;
     int id = tok[t];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
     const TW* src = table + (size_t)id * W;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) x[(size_t)t * W + i] = wload<TW>(src + i);
+    const int i0 = (blockIdx.y * 256 + threadIdx.x) * 4;
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = i0 + j < W ? wload<TW>(src + i0 + j) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        if (i0 + j < W) x[(size_t)t * W + i0 + j] = v[j];
 }
 
 __device__ __forceinline__ float block_sum256(float v, float* red) {
@@ -42,16 +48,29 @@ struct NormArgs {
     float* out; int W; int add;
 };
 
+constexpr int TOPMAX = 64;          // (token, slot) rows staged in shared memory; beyond that they are re-read
+
 __global__ void __launch_bounds__(256) combine_norm_kernel(NormArgs a) {
     extern __shared__ float y[];
     __shared__ float red[8];
+    __shared__ float wk[TOPMAX];
+    __shared__ long long pk[TOPMAX];
     const int t = blockIdx.x;
     const size_t srow = a.src_rows ? (size_t)a.src_rows[t] : (size_t)t;
+    const int top = a.top;
+    if (threadIdx.x < top && threadIdx.x < TOPMAX) {
+        wk[threadIdx.x] = a.w[(size_t)t * top + threadIdx.x];
+        pk[threadIdx.x] = (long long)a.inv[(size_t)t * top + threadIdx.x] * a.W;
+    }
+    if (top > 0) __syncthreads();
     float s = 0.f;
     for (int i = threadIdx.x; i < a.W; i += blockDim.x) {
         float v = 0.f;
-        for (int k = 0; k < a.top; ++k)
-            v = fmaf(a.w[(size_t)t * a.top + k], a.parts[(size_t)a.inv[(size_t)t * a.top + k] * a.W + i], v);
+        const int ks = top < TOPMAX ? top : TOPMAX;
+#pragma unroll 8
+        for (int k = 0; k < ks; ++k) v = fmaf(wk[k], a.parts[pk[k] + i], v);
+        for (int k = TOPMAX; k < top; ++k)
+            v = fmaf(a.w[(size_t)t * top + k], a.parts[(size_t)a.inv[(size_t)t * top + k] * a.W + i], v);
         if (a.base) v += a.base[srow * a.W + i];
         y[i] = v;
         s += v;
@@ -70,7 +89,7 @@ __global__ void __launch_bounds__(256) combine_norm_kernel(NormArgs a) {
 
 // ---------------------------------------------------------------- router
 struct RouteArgs {
-    const float* x; int ldx; const void* Wr; int W, E, top, gcount, gkeep;
+    const float* z; int ldz; int T, E, top, gcount, gkeep;
     int* idx; float* wt; int* rank; int* counts;
 };
 
@@ -83,30 +102,23 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
     }
 }
 
-template <typename TW>
-__global__ void __launch_bounds__(128) moe_route_kernel(RouteArgs a) {
+constexpr int ROUTE_WARPS = 4;       // tokens per block, one warp each
+
+__global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(RouteArgs a) {
     extern __shared__ float sm[];
-    float* s = sm;                       // [E] logits, then scores
-    float* gs = s + a.E;                 // [gcount]
-    int* open = (int*)(gs + a.gcount);   // [E] 1 = may still be chosen
-    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const float* x = a.x + (size_t)t * a.ldx;
-    for (int e = warp; e < a.E; e += 4) {
-        const TW* w = (const TW*)a.Wr + (size_t)e * a.W;
-        float acc = 0.f;
-        for (int k = lane; k < a.W; k += 32) acc = fmaf(x[k], wload<TW>(w + k), acc);
-        acc = warp_sum(acc);
-        if (lane == 0) s[e] = acc;
-    }
-    __syncthreads();
-    if (warp != 0) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * ROUTE_WARPS + warp;
+    if (t >= a.T) return;
+    float* s = sm + (size_t)warp * (2 * a.E + a.gcount);     // [E] scores
+    float* gs = s + a.E;                                      // [gcount]
+    int* open = (int*)(gs + a.gcount);                        // [E] 1 = may still be chosen
+    const float* z = a.z + (size_t)t * a.ldz;
     float mx = -INFINITY;
-    for (int e = lane; e < a.E; e += 32) mx = fmaxf(mx, s[e]);
+    for (int e = lane; e < a.E; e += 32) { const float v = z[e]; s[e] = v; mx = fmaxf(mx, v); }
     mx = warp_max(mx);
     float sum = 0.f;
     for (int e = lane; e < a.E; e += 32) { const float p = expf(s[e] - mx); s[e] = p; sum += p; }
     sum = warp_sum(sum);
-    __syncwarp();
     for (int e = lane; e < a.E; e += 32) { s[e] = s[e] / sum; open[e] = 1; }
     __syncwarp();
     if (a.gcount > 1 && a.gkeep < a.gcount) {
@@ -116,7 +128,6 @@ __global__ void __launch_bounds__(128) moe_route_kernel(RouteArgs a) {
             for (int j = 0; j < per; ++j) b = fmaxf(b, s[g * per + j]);
             gs[g] = b;
         }
-        __syncwarp();
         for (int e = lane; e < a.E; e += 32) open[e] = 0;
         __syncwarp();
         for (int it = 0; it < a.gkeep; ++it) {
@@ -182,8 +193,8 @@ extern "C" {
 int pgk_embed_rows_f32(const void* table, int wdt, const int32_t* tokens, float* x, int n, int width, int vocab, void* stream) {
     PGK_REQUIRE(wdt == 0 || wdt == 2, "embed_rows_f32 failed: table must be float32 (0) or bfloat16 (2), got %d", wdt);
     if (n <= 0) return 0;
-    if (wdt == 2) PGK_CUDA(launch(embed_rows_kernel<uint16_t>, dim3(n), dim3(128), 0, (cudaStream_t)stream, (const uint16_t*)table, tokens, x, width, vocab));
-    else PGK_CUDA(launch(embed_rows_kernel<float>, dim3(n), dim3(128), 0, (cudaStream_t)stream, (const float*)table, tokens, x, width, vocab));
+    if (wdt == 2) PGK_CUDA(launch(embed_rows_kernel<uint16_t>, dim3(n, (width + 1023) / 1024), dim3(256), 0, (cudaStream_t)stream, (const uint16_t*)table, tokens, x, width, vocab));
+    else PGK_CUDA(launch(embed_rows_kernel<float>, dim3(n, (width + 1023) / 1024), dim3(256), 0, (cudaStream_t)stream, (const float*)table, tokens, x, width, vocab));
     return 0;
 }
 
@@ -204,21 +215,19 @@ int pgk_combine_layernorm_f32(const float* base, const int32_t* src_rows, const 
     return 0;
 }
 
-int pgk_moe_route_grouped(const float* x, int ldx, const void* router, int wdt, int tokens, int width, int experts, int top,
-                          int group_count, int group_keep, int32_t* idx, float* weights, int32_t* rank, int32_t* counts,
-                          void* stream) {
-    PGK_REQUIRE(wdt == 0 || wdt == 2, "moe_route_grouped failed: router must be float32 (0) or bfloat16 (2), got %d", wdt);
+int pgk_moe_route_grouped(const float* logits, int ld, int tokens, int experts, int top, int group_count, int group_keep,
+                          int32_t* idx, float* weights, int32_t* rank, int32_t* counts, void* stream) {
     PGK_REQUIRE(experts > 0 && top > 0 && top <= experts, "moe_route_grouped failed: top %d of %d experts", top, experts);
     if (group_count < 1) group_count = 1;
     PGK_REQUIRE(experts % group_count == 0 && group_keep >= 1, "moe_route_grouped failed: %d experts in %d groups (keep %d)", experts, group_count, group_keep);
     PGK_REQUIRE(group_count == 1 || group_keep >= group_count || (experts / group_count) * group_keep >= top,
                 "moe_route_grouped failed: %d kept groups hold fewer than top = %d experts", group_keep, top);
     if (tokens <= 0) return 0;
-    RouteArgs a{x, ldx, router, width, experts, top, group_count, group_keep, idx, weights, rank, counts};
-    const size_t smem = (size_t)(2 * experts + group_count) * 4;
+    RouteArgs a{logits, ld, tokens, experts, top, group_count, group_keep, idx, weights, rank, counts};
+    const size_t smem = (size_t)ROUTE_WARPS * (2 * experts + group_count) * 4;
     PGK_REQUIRE(smem <= 48 * 1024, "moe_route_grouped failed: too many experts (%d)", experts);
-    if (wdt == 2) PGK_CUDA(launch(moe_route_kernel<uint16_t>, dim3(tokens), dim3(128), smem, (cudaStream_t)stream, a));
-    else PGK_CUDA(launch(moe_route_kernel<float>, dim3(tokens), dim3(128), smem, (cudaStream_t)stream, a));
+    PGK_CUDA(launch(moe_route_kernel, dim3((tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem,
+                    (cudaStream_t)stream, a));
     return 0;
 }
 

@@ -16,7 +16,7 @@ from .loader import (load_gpt2_from_safetensors, load_llama_from_safetensors, lo
                      load_model_from_safetensors, load_qwen3_from_safetensors, save_model_to_safetensors)
 from .loader_layered import build_layered_model, load_layered_model
 from .paged_cache import PagedKVCache, PagePool
-from .random_init import build_random_model
+from .random_init import build_random_model, random_layered_model
 from .safetensors import SafeTensorsFile, TensorInfo, load_safetensors, save_safetensors
 from .sampling import sample_token
 from .tp import TensorParallel, shard_plan, shard_range

@@ -1,7 +1,8 @@
 """Mixture of experts of the token-major models (net-new; beside `MoELayer`, whose router is top-k then softmax over
 the chosen logits and whose experts are FP8 / NVF4 GEMVs on bfloat16 rows).
 
-Router (pgk_moe_route_grouped): softmax over ALL experts, optional group limit (only members of the best
+Router: float32 logits from the router GEMM (bfloat16 products are exact in float32), then pgk_moe_route_grouped:
+softmax over ALL experts, optional group limit (only members of the best
 `group_keep` of `group_count` groups of neighbours), the `top` largest scores, renormalised.  Experts: stacked
 [E, 2 ff, W] gate/up pairs (SiLU * up in the GEMM epilogue) and [E, W, ff] down matrices.
 
@@ -24,8 +25,7 @@ from .linear import LinearRows
 class GroupedRouterMoE:
     def __init__(self, spec: MoESpec, router: GPUArray, gate_up: LinearRows, down: LinearRows,
                  shared_gate_up: LinearRows | None = None, shared_down: LinearRows | None = None):
-        self.spec, self.router = spec, router
-        self.router_dt = 2 if router.dtype.name == "bfloat16" else 0
+        self.spec, self.router = spec, LinearRows(router)
         self.gate_up, self.down = gate_up, down
         self.shared_gate_up, self.shared_down = shared_gate_up, shared_down
         if gate_up.groups != spec.experts or down.groups != spec.experts:
@@ -44,7 +44,8 @@ class GroupedRouterMoE:
         sp, T, b = self.spec, ctx.T, ctx.buf
         W, top, ff = self.gate_up.in_features, sp.top, sp.ff
         few = T <= LinearRows.FEW
-        api.moe_route_grouped(x.device_ptr, W, self.router.device_ptr, self.router_dt, T, W, sp.experts, top,
+        self.router.forward(x.device_ptr, W, T, b.moe_z.device_ptr, sp.experts)       # float32 logits [T, E]
+        api.moe_route_grouped(b.moe_z.device_ptr, sp.experts, T, sp.experts, top,
                               sp.group_count, sp.group_keep, b.moe_idx.device_ptr, b.moe_w.device_ptr,
                               None if few else b.moe_rank.device_ptr, None if few else b.moe_counts.device_ptr, _st())
         if few:

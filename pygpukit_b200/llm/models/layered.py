@@ -15,12 +15,14 @@ The step function is the only forward pass; `generate`, the scheduler and bin/tr
 """
 from __future__ import annotations
 
+import os
+
 import numpy as np
 
 from ..._lib import api
 from ...core.array import GPUArray
 from ...core.dtypes import float32, int32
-from ...core.stream import current_stream_handle as _st
+from ...core.stream import CudaGraph, Stream, current_stream_handle as _st
 from ..buffers import RowBuffers
 from ..config import LayeredConfig
 from ..layers.block import PostNormBlock
@@ -50,6 +52,8 @@ class StepContext:
             seqs.append((row, n, slot, pos0))
             row += n
         self.T, self.n_want = row, len(want_rows)
+        self._seqs, self._model = seqs, model
+        self.decode_only = all(n == 1 and p0 > 0 for _, n, _, p0 in seqs)
         parts = [np.asarray(toks, np.int32), np.asarray(slots, np.int32), np.asarray(poss, np.int32),
                  np.asarray(want_rows, np.int32)]
         off = {"tok": 0, "slot": self.T, "pos": 2 * self.T, "want": 3 * self.T}
@@ -82,6 +86,13 @@ class StepContext:
         self.cache = cache
         self.buf = model._buffers(self.T)
 
+    def max_keys(self, chunk: int) -> int:
+        """The longest key range any sequence of the step reads under a chunk size (0: none)."""
+        return max(p0 + n - ((p0 // chunk) * chunk if chunk > 0 else 0) for _, n, _, p0 in self._seqs)
+
+    def workspace(self, n_floats: int) -> GPUArray:
+        return self._model._workspace(n_floats)
+
     def tiles(self, queries_per_tile: int) -> tuple[int, int]:
         off, n = self._tiles_off[queries_per_tile]
         return self._base + 4 * off, n
@@ -102,6 +113,11 @@ class LayeredCausalModel:
         self._buf: RowBuffers | None = None
         self._meta: GPUArray | None = None
         self._out: GPUArray | None = None
+        self._ws: GPUArray | None = None
+        self.use_graphs = os.environ.get("PGK_LAYERED_GRAPH", "1") != "0"
+        self._graphs: dict = {}
+        self._graph_warm: set = set()
+        self._gstream: Stream | None = None
         self._tile_sizes = {b.mixer.queries_per_tile for b in blocks}
         self._tops = {b.mlp.spec.top for b in blocks if b.mlp is not None}
 
@@ -110,6 +126,8 @@ class LayeredCausalModel:
         """Allocate the paged cache for about `max_tokens` live positions (it grows when more arrive)."""
         shapes = [(b.mixer.spec.kv_heads, b.mixer.spec.dim, b.mixer.spec.vdim) for b in self.blocks]
         self.cache = PagedKVCache(shapes, self.dtype, page_size, max_tokens, slots)
+        self._graphs.clear()
+        self._graph_warm.clear()
         return self.cache
 
     def _buffers(self, rows: int) -> RowBuffers:
@@ -117,38 +135,78 @@ class LayeredCausalModel:
             self._buf = RowBuffers(self.config, max(rows, 2 * self._buf.rows if self._buf else 0))
         return self._buf
 
+    def _workspace(self, n_floats: int) -> GPUArray:
+        if self._ws is None or self._ws.size < n_floats:
+            self._ws = GPUArray((max(1 << 20, 2 * n_floats),), float32)
+        return self._ws
+
     def _meta_buffer(self, n: int) -> GPUArray:
         if self._meta is None or self._meta.size < n:
             self._meta = GPUArray((max(1024, 2 * n),), int32)
         return self._meta
 
     # ------------------------------------------------------------------ the step
-    def step_device(self, entries, end=()) -> tuple[GPUArray | None, int]:
-        """Run one ragged batch; returns (float32 logits [n_want, vocab] on the device or None, n_want).  `end` names
-        the requests whose cache is given back after the step."""
-        if self.cache is None:
-            self.init_cache()
+    def _forward(self, ctx: StepContext) -> None:
+        """Every launch of a step: embedding, the blocks, final norm + head of the wanted rows (into self._out)."""
         cfg = self.config
         W, V = cfg.hidden_size, cfg.vocab_size
-        ctx = StepContext(self, entries, self._tile_sizes, self._tops)
         b, T = ctx.buf, ctx.T
         x = b.x
         api.embed_rows_f32(self.embed_tokens.device_ptr, self.embed_dt, ctx.tok_ptr, x.device_ptr, T, W, V, _st())
         for blk in self.blocks:
             blk.forward(ctx, x)
-        out = None
         if ctx.n_want:
             n = ctx.n_want
-            if self._out is None or self._out.shape[0] < n:
-                self._out = GPUArray((max(n, 16), V), float32)
             xn = b.y                                   # free after the last block
             api.combine_layernorm_f32(x.device_ptr, ctx.want_ptr, None, None, None, 0, self.final_norm[0].device_ptr,
                                       self.final_norm[1].device_ptr, cfg.norm_eps, xn.device_ptr, n, W, 0, _st())
             self.lm_head.forward(xn.device_ptr, W, n, self._out.device_ptr, V)
-            out = self._out
+
+    def _graph_key(self, ctx: StepContext):
+        """Decode steps (one token per request, few requests) replay a captured CUDA graph: the step's description
+        lives in device buffers whose addresses, and every launch shape, are fixed by this key."""
+        if not self.use_graphs or ctx.T > LinearRows.FEW or not ctx.decode_only:
+            return None
+        c = self.cache
+        return (ctx.T, ctx.n_want, c.pool.max_pages, c.table_dev.device_ptr, c.k[0].device_ptr, id(ctx.buf),
+                self._meta.device_ptr, self._out.device_ptr, self._ws.device_ptr if self._ws is not None else 0,
+                tuple(blk.mixer.key_slices(ctx) for blk in self.blocks))
+
+    def step_device(self, entries, end=()) -> tuple[GPUArray | None, int]:
+        """Run one ragged batch; returns (float32 logits [n_want, vocab] on the device or None, n_want).  `end` names
+        the requests whose cache is given back after the step."""
+        if self.cache is None:
+            self.init_cache()
+        V = self.config.vocab_size
+        ctx = StepContext(self, entries, self._tile_sizes, self._tops)
+        if self._out is None or self._out.shape[0] < max(ctx.n_want, 1):
+            self._out = GPUArray((max(ctx.n_want, 16), V), float32)
+        key = self._graph_key(ctx)
+        if key is None:
+            self._forward(ctx)
+        else:
+            g = self._graphs.get(key)
+            if g is None and key not in self._graph_warm:
+                self._graph_warm.add(key)              # first sight: run eagerly (kernel attributes, workspaces)
+                self._forward(ctx)
+                if self._graph_key(ctx) != key:        # the eager run grew a workspace: forget the stale key
+                    self._graph_warm.discard(key)
+            else:
+                if self._gstream is None:
+                    self._gstream = Stream()
+                if g is None:
+                    if len(self._graphs) >= 64:
+                        self._graphs.clear()
+                    g = CudaGraph()
+                    api.device_sync()
+                    with g.capture(self._gstream):
+                        self._forward(ctx)
+                    self._graphs[key] = g
+                g.replay(self._gstream)
+                self._gstream.synchronize()
         for seq_id in end:
             self.cache.release(seq_id)
-        return out, ctx.n_want
+        return (self._out if ctx.n_want else None), ctx.n_want
 
     def step(self, entries, end=()) -> np.ndarray:
         """`step_device` with the wanted logits copied to the host ([n_want, vocab] float32)."""

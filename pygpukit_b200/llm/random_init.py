@@ -285,3 +285,47 @@ def _moe(mk: _Maker, config: TransformerConfig, L: int, H: int, world: int, rank
 
 
 __all__ = ["build_random_model", "normal_bf16", "quantize_fp8", "quantize_nvf4"]
+
+
+def random_layered_model(config, dtype: str = "bfloat16", seed: int = 1234, std: float = 0.02, v_lambda: float = 0.5):
+    """A layered model (`LayeredConfig`) with N(0, std^2) matrices drawn on the device, unit norm weights and zero
+    biases -- benchmark-sized models in seconds.  bfloat16 matrices only (float32 models are built from host
+    tensors, loader_layered.build_layered_model)."""
+    from ..core.dtypes import float32
+    from .layers.block import PostNormBlock
+    from .layers.linear import LinearRows
+    from .layers.moe_rows import GroupedRouterMoE
+    from .layers.paged_attention import PagedAttentionMixer
+    from .models.layered import LayeredCausalModel
+    if dtype != "bfloat16":
+        raise ValueError("random_layered_model draws bfloat16 matrices")
+    W, V, eps = config.hidden_size, config.vocab_size, config.norm_eps
+    n = [0]
+
+    def mat(*shape):
+        n[0] += 1
+        return normal_bf16(shape, (seed * 1000003 + n[0] * 8191) & 0x7FFFFFFF, std)
+
+    def vec(size, value):
+        return from_numpy(np.full((size,), value, np.float32))
+
+    blocks, mixing = [], False
+    for i, L in enumerate(config.layers):
+        m = L.mixer
+        cols = m.heads * m.dim + m.kv_heads * (m.dim + m.vdim) + (m.heads * m.vdim if m.out_gate else 0)
+        role = 0 if not m.v_mix else (2 if mixing else 1)
+        mixing = mixing or m.v_mix
+        mixer = PagedAttentionMixer(m, i, LinearRows(mat(cols, W)), LinearRows(mat(W, m.heads * m.vdim)), vec(m.dim, 1.0),
+                                    vec(m.dim, 1.0), eps, role, v_lambda)
+        mlp = norm2 = None
+        if L.mlp is not None:
+            f = L.mlp
+            sgu = LinearRows(mat(2 * f.shared_ff, W), epilogue=1) if f.shared_ff else None
+            sdn = LinearRows(mat(W, f.shared_ff)) if f.shared_ff else None
+            mlp = GroupedRouterMoE(f, mat(f.experts, W), LinearRows(mat(f.experts, 2 * f.ff, W), epilogue=1),
+                                   LinearRows(mat(f.experts, W, f.ff)), sgu, sdn)
+            norm2 = (vec(W, 1.0), vec(W, 0.0))
+        blocks.append(PostNormBlock(mixer, (vec(W, 1.0), vec(W, 0.0)), mlp, norm2, eps))
+    head = LinearRows(mat(V, W), epilogue=2, scale=config.logit_scale, cap=config.logit_softcap)
+    _ = float32
+    return LayeredCausalModel(config, mat(V, W), blocks, (vec(W, 1.0), vec(W, 0.0)), head, dtype)

@@ -124,13 +124,15 @@ def test_gemm_grouped_and_per_row(wdt):
 def test_router_and_row_lists(E, top, gc, keep, wdt):
     rng = np.random.default_rng(E + top)
     T, W = 37, 24
-    x = rng.standard_normal((T, W)).astype(np.float32)
+    x = bf16_round(rng.standard_normal((T, W)).astype(np.float32))
     Wr = bf16_round(rng.standard_normal((E, W)).astype(np.float32) * 0.8)
     ridx, rw = R.route(x.astype(np.float64) @ Wr.astype(np.float64).T, top, gc, keep)
     idx, wt, rank = gk.zeros((T * top,), gk.int32), gk.zeros((T * top,), gk.float32), gk.zeros((T * top,), gk.int32)
     counts = gk.zeros((E,), gk.int32)
-    api.moe_route_grouped(f32(x).device_ptr, W, dev_w(Wr, wdt).device_ptr, wdt, T, W, E, top, gc, keep,
-                          idx.device_ptr, wt.device_ptr, rank.device_ptr, counts.device_ptr, None)
+    z = gk.zeros((T, E), gk.float32)
+    llm.LinearRows(dev_w(Wr, wdt)).forward(f32(x).device_ptr, W, T, z.device_ptr, E)
+    api.moe_route_grouped(z.device_ptr, E, T, E, top, gc, keep, idx.device_ptr, wt.device_ptr, rank.device_ptr,
+                          counts.device_ptr, None)
     got_idx = idx.to_numpy().reshape(T, top)
     assert np.array_equal(got_idx, ridx)
     assert np.abs(wt.to_numpy().reshape(T, top) - rw).max() < 1e-5
@@ -175,7 +177,8 @@ class AttnHarness:
     """mixer_prep + attention on raw q / k / v rows (norm weights one, eps zero would change q: the oracle side applies
     the same RMS norm)."""
 
-    def __init__(self, H, G, D, Dv, chunk, scale=0.3, softcap=0.0, page=4, dtype="float32", gate=False):
+    def __init__(self, H, G, D, Dv, chunk, scale=0.3, softcap=0.0, page=4, dtype="float32", gate=False, splits=1):
+        self.splits = splits
         self.H, self.G, self.D, self.Dv, self.chunk, self.scale, self.softcap, self.gate = H, G, D, Dv, chunk, scale, softcap, gate
         self.cache = PagedKVCache([(G, D, Dv)], dtype, page, 64, 2)
         self.qt = api.seq_queries_per_tile(H, G)
@@ -200,7 +203,8 @@ class AttnHarness:
         api.seq_attention(proj.device_ptr, self.cols, 0, self.H * self.D + self.G * self.D + self.G * self.Dv, out.device_ptr,
                           self.H * self.Dv, c.k[0].device_ptr, c.v[0].device_ptr, c.dtype_code, c.table_dev.device_ptr,
                           c.pool.max_pages, c.page_size, i32(tiles).device_ptr, len(tiles), self.slopes.device_ptr, self.H,
-                          self.G, self.D, self.Dv, self.chunk, self.scale, self.softcap, 1 if self.gate else 0, None)
+                          self.G, self.D, self.Dv, self.chunk, self.scale, self.softcap, 1 if self.gate else 0, self.splits,
+                          keep(gk.zeros((n * self.H * self.splits * (self.Dv + 2),), gk.float32)).device_ptr, n, None)
         return out.to_numpy().reshape(n, self.H, self.Dv)
 
     def oracle(self, q, k, v, gate=None):
@@ -281,6 +285,19 @@ def test_attention_far_key_among_hundreds_and_across_page_borders():
     assert np.abs(got - ref).max() < 1e-5
     assert got[299, 0, 3] > 1.0 and got[299, 0, 0] > 1.0 and got[299, 0, 7] > 1.0   # all three far keys count at the end
     assert got[100, 0, 7] < 0.1                                          # key 127 is in the future of query 100
+
+
+@pytest.mark.parametrize("splits", [2, 3, 7])
+def test_attention_key_slices_fold_to_the_same_answer(splits):
+    H, G, D, Dv, T = 4, 2, 16, 40, 200
+    rng = np.random.default_rng(splits)
+    q, k = rng.standard_normal((T, H, D)), rng.standard_normal((T, G, D))
+    v, gate = rng.standard_normal((T, G, Dv)), rng.standard_normal((T, H, Dv))
+    h = AttnHarness(H, G, D, Dv, chunk=90, softcap=4.0, page=16, gate=True, splits=splits)
+    ref = h.oracle(q, k, v, gate)
+    got = np.concatenate([h.run("a", q[:150], k[:150], v[:150], gate[:150])] +
+                         [h.run("a", q[i:i + 1], k[i:i + 1], v[i:i + 1], gate[i:i + 1]) for i in range(150, T)])
+    assert np.abs(got - ref).max() < 1e-5
 
 
 def test_value_mixing_records_and_mixes():
@@ -430,6 +447,16 @@ def test_long_decoding_and_wanted_places_subset():
     assert np.abs(got - ref[want]).max() < F32_TOL
     got = np.concatenate([m.step([("a", [t], [0])]) for t in toks[70:]])
     assert np.abs(got - ref[70:]).max() < F32_TOL
+
+
+def test_decoding_over_a_long_unchunked_context_reads_the_cache_in_slices():
+    cfg, P, m = make("all_groups_kept_odd_width", page=16, tokens_hint=512)      # chunk 0: every key stays visible
+    toks = tokens(cfg, 300, seed=8)
+    ref = R.forward(cfg, P, toks)
+    m.step([("a", toks[:288], [])])
+    got = np.concatenate([m.step([("a", [t], [0])]) for t in toks[288:]])
+    assert m._ws is not None                                             # the sliced path ran
+    assert np.abs(got - ref[288:]).max() < F32_TOL
 
 
 @pytest.mark.parametrize("name", ["base", "mixed_stack", "all_groups_kept_odd_width"])
