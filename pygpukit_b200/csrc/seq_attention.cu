@@ -78,6 +78,7 @@ struct AttnArgs {
     int H, G, D, Dv, chunk, HB, gate;
     float scale, cap;
     int splits; float* ws;              // splits > 1: partial (m, l, acc[Dv]) records [row][H][splits][Dv + 2]
+    unsigned* tickets;                  // one arrival counter per (tile, head block), zero between launches
 };
 
 constexpr int KT = 32;                  // keys per tile = one per lane
@@ -228,6 +229,7 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
         }
     }
     if (a.splits > 1) {
+        // every slice leaves (max, sum, P.V) records; the block that arrives last folds them (threadfence + ticket)
 #pragma unroll
         for (int c = 0; c < PPW; ++c) {
             if (!ok[c]) continue;
@@ -236,6 +238,60 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
 #pragma unroll
             for (int v = 0; v < NV; ++v)
                 if (lane + 32 * v < Dv) rec[2 + lane + 32 * v] = acc[c][v];
+        }
+        __shared__ unsigned last;
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned* tk = a.tickets + (size_t)blockIdx.x * gridDim.y + blockIdx.y;
+            const unsigned n = atomicAdd(tk, 1u);
+            last = (n == (unsigned)a.splits - 1u);
+            if (last) *tk = 0u;
+        }
+        __syncthreads();
+        if (!last) return;
+        __threadfence();
+        // fold, phase 1: per pair the slices' weights exp(m_s - M) / L (lanes over slices)
+        __shared__ float wsl[NWARP * PPW][64];
+#pragma unroll
+        for (int c = 0; c < PPW; ++c) {
+            if (!ok[c]) continue;
+            const float* rec = a.ws + (((size_t)(t0 + qi[c]) * a.H + hd[c]) * a.splits) * (Dv + 2);
+            float ms[2], ls[2], M = -INFINITY;
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int sp = lane + 32 * u;
+                ms[u] = sp < a.splits ? __ldcg(rec + (size_t)sp * (Dv + 2)) : -INFINITY;
+                ls[u] = sp < a.splits ? __ldcg(rec + (size_t)sp * (Dv + 2) + 1) : 0.f;
+                M = fmaxf(M, ms[u]);
+            }
+            M = warp_max(M);
+            float e[2], L = 0.f;
+#pragma unroll
+            for (int u = 0; u < 2; ++u) { e[u] = ms[u] == -INFINITY ? 0.f : expf(ms[u] - M); L += ls[u] * e[u]; }
+            L = warp_sum(L);
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+                if (lane + 32 * u < a.splits) wsl[warp * PPW + c][lane + 32 * u] = e[u] * inv;
+        }
+        __syncthreads();
+        // phase 2: every thread of the block takes outputs (pair, dv); the slices' loads are independent
+        for (int i = threadIdx.x; i < NWARP * PPW * Dv; i += blockDim.x) {
+            const int p = i / Dv, dv = i - p * Dv;
+            const int q = p / a.HB, hh = p - q * a.HB;
+            if (q >= nq || hh >= nh) continue;
+            const size_t t = t0 + q;
+            const int h = hb0 + hh;
+            const float* rec = a.ws + ((t * a.H + h) * a.splits) * (Dv + 2) + 2 + dv;
+            float o = 0.f;
+#pragma unroll 8
+            for (int sp = 0; sp < a.splits; ++sp) o = fmaf(wsl[p][sp], __ldcg(rec + (size_t)sp * (Dv + 2)), o);
+            if (a.gate) {
+                const float z = a.proj[t * a.ld + a.g_off + (size_t)h * Dv + dv];
+                o *= 1.f / (1.f + expf(-z));
+            }
+            a.out[t * a.ldo + (size_t)h * Dv + dv] = o;
         }
         return;
     }
@@ -255,37 +311,6 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
             }
             a.out[t * a.ldo + (size_t)hd[c] * Dv + dv] = o;
         }
-    }
-}
-
-// fold the partial records of the key slices: one warp per (row, head)
-__global__ void __launch_bounds__(128) seq_attention_merge_kernel(AttnArgs a, int rows) {
-    const int lane = threadIdx.x & 31, w = blockIdx.x * 4 + (threadIdx.x >> 5);
-    if (w >= rows * a.H) return;
-    const int t = w / a.H, h = w - t * a.H, Dv = a.Dv;
-    const float* rec = a.ws + (size_t)w * a.splits * (Dv + 2);
-    float M = -INFINITY;
-    for (int s = lane; s < a.splits; s += 32) M = fmaxf(M, rec[(size_t)s * (Dv + 2)]);
-    M = warp_max(M);
-    float L = 0.f;
-    for (int s = lane; s < a.splits; s += 32) {
-        const float ms = rec[(size_t)s * (Dv + 2)];
-        if (ms != -INFINITY) L += rec[(size_t)s * (Dv + 2) + 1] * expf(ms - M);
-    }
-    L = warp_sum(L);
-    const float inv = L > 0.f ? 1.f / L : 0.f;
-    for (int dv = lane; dv < Dv; dv += 32) {
-        float o = 0.f;
-        for (int s = 0; s < a.splits; ++s) {
-            const float ms = rec[(size_t)s * (Dv + 2)];
-            if (ms != -INFINITY) o = fmaf(rec[(size_t)s * (Dv + 2) + 2 + dv], expf(ms - M), o);
-        }
-        o *= inv;
-        if (a.gate) {
-            const float z = a.proj[(size_t)t * a.ld + a.g_off + (size_t)h * Dv + dv];
-            o *= 1.f / (1.f + expf(-z));
-        }
-        a.out[(size_t)t * a.ldo + (size_t)h * Dv + dv] = o;
     }
 }
 
@@ -342,18 +367,18 @@ int pgk_seq_mixer_prep(float* proj, int ld, int tokens, int heads, int kv_heads,
 int pgk_seq_attention(const float* proj, int ld, int q_off, int gate_off, float* out, int ldo, const void* k_cache,
                       const void* v_cache, int cache_dtype, const int32_t* table, int max_pages, int page_size,
                       const int32_t* tiles, int n_tiles, const float* slopes, int heads, int kv_heads, int dim, int vdim,
-                      int chunk, float scale, float softcap, int gate, int splits, float* workspace, int rows, void* stream) {
+                      int chunk, float scale, float softcap, int gate, int splits, float* workspace, uint32_t* tickets,
+                      void* stream) {
     PGK_REQUIRE(cache_dtype == 0 || cache_dtype == 2, "seq_attention failed: the cache is float32 (0) or bfloat16 (2), got %d", cache_dtype);
     PGK_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0, "seq_attention failed: invalid head layout");
-    PGK_REQUIRE(splits >= 1 && splits <= 64 && (splits == 1 || workspace), "seq_attention failed: 1..64 key slices, more than one needs the workspace");
+    PGK_REQUIRE(splits >= 1 && splits <= 64 && (splits == 1 || (workspace && tickets)),
+                "seq_attention failed: 1..64 key slices, more than one needs the workspace and the tickets");
     if (n_tiles <= 0) return 0;
     AttnArgs a{proj, ld, q_off, gate_off, out, ldo, k_cache, v_cache, table, max_pages, page_size, (const int4*)tiles, slopes,
-               heads, kv_heads, dim, vdim, chunk, pgk_seq_heads_per_block(heads, kv_heads), gate, scale, softcap, splits, workspace};
-    const int rc = cache_dtype == 2 ? launch_attn_nv<uint16_t>(a, n_tiles, (cudaStream_t)stream)
-                                    : launch_attn_nv<float>(a, n_tiles, (cudaStream_t)stream);
-    if (rc || splits == 1) return rc;
-    PGK_CUDA(launch(seq_attention_merge_kernel, dim3((rows * heads + 3) / 4), dim3(128), 0, (cudaStream_t)stream, a, rows));
-    return 0;
+               heads, kv_heads, dim, vdim, chunk, pgk_seq_heads_per_block(heads, kv_heads), gate, scale, softcap, splits, workspace,
+               tickets};
+    return cache_dtype == 2 ? launch_attn_nv<uint16_t>(a, n_tiles, (cudaStream_t)stream)
+                            : launch_attn_nv<float>(a, n_tiles, (cudaStream_t)stream);
 }
 
 }  // extern "C"

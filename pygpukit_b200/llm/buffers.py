@@ -109,6 +109,7 @@ class RowBuffers:
         self.moe_inv = GPUArray((R * top,), int32)
         self.moe_w = GPUArray((R * top,), float32)
         self.moe_z = GPUArray((R, experts), float32)         # router logits
+        self.tickets = zeros((4096,), int32)                # arrival counters of the key-sliced attention (self-clearing)
         self.moe_counts = zeros((experts,), int32)          # zero between uses (pgk_moe_row_lists clears it)
         self.moe_off = GPUArray((experts + 1,), int32)
         self.moe_act = GPUArray((R * top, ff), float32)

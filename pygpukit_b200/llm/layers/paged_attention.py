@@ -50,8 +50,8 @@ class PagedAttentionMixer:
         keys = ctx.max_keys(s.chunk)
         if blocks >= 148 or keys < 256:
             return 1
-        want = max(1, min(64, keys // 32, 592 // blocks))
-        return 1 << (want.bit_length() - 1)
+        want = max(1, min(64, -(-keys // 32), 592 // blocks))
+        return min(64, 1 << (want - 1).bit_length())
 
     def forward(self, ctx, x: GPUArray, out: GPUArray) -> None:
         """x [T, W] -> out [T, W] (the mixer's output before the block's norm); K / V of the T tokens enter the cache."""
@@ -69,14 +69,15 @@ class PagedAttentionMixer:
                            ctx.slot_ptr, ctx.pos_ptr, _st())
         tiles_ptr, n_tiles = ctx.tiles(self.queries_per_tile)
         ldo = s.heads * s.vdim
-        splits, ws = self.key_slices(ctx), None
+        splits, ws, tickets = self.key_slices(ctx), None, None
         if splits > 1:
             ws = ctx.workspace(T * s.heads * splits * (s.vdim + 2)).device_ptr
+            tickets = ctx.buf.tickets.device_ptr
         api.seq_attention(proj.device_ptr, ld, 0, self.q_cols + self.k_cols + self.v_cols, attn.device_ptr, ldo,
                           kc.device_ptr, vc.device_ptr, cache.dtype_code, cache.table_dev.device_ptr, cache.pool.max_pages,
                           cache.page_size, tiles_ptr, n_tiles, self.slopes.device_ptr if self.slopes is not None else None,
                           s.heads, s.kv_heads, s.dim, s.vdim, s.chunk, s.scale, s.softcap, 1 if s.out_gate else 0,
-                          splits, ws, T, _st())
+                          splits, ws, tickets, _st())
         self.o_proj.forward(attn.device_ptr, ldo, T, out.device_ptr, self.o_proj.out_features)
 
 

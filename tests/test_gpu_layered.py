@@ -184,6 +184,7 @@ class AttnHarness:
         self.qt = api.seq_queries_per_tile(H, G)
         self.slopes = gk.from_numpy(R.head_slopes(H).astype(np.float32))
         self.ones = gk.from_numpy(np.ones(D, np.float32))
+        self.tickets = gk.zeros((4096,), gk.int32)
         self.cols = H * D + G * D + G * Dv + (H * Dv if gate else 0)
 
     def run(self, seq, q, k, v, gate=None):
@@ -204,7 +205,9 @@ class AttnHarness:
                           self.H * self.Dv, c.k[0].device_ptr, c.v[0].device_ptr, c.dtype_code, c.table_dev.device_ptr,
                           c.pool.max_pages, c.page_size, i32(tiles).device_ptr, len(tiles), self.slopes.device_ptr, self.H,
                           self.G, self.D, self.Dv, self.chunk, self.scale, self.softcap, 1 if self.gate else 0, self.splits,
-                          keep(gk.zeros((n * self.H * self.splits * (self.Dv + 2),), gk.float32)).device_ptr, n, None)
+                          keep(gk.zeros((n * self.H * self.splits * (self.Dv + 2),), gk.float32)).device_ptr,
+                          self.tickets.device_ptr, None)
+        assert not self.tickets.to_numpy().any()                         # the tickets clear themselves
         return out.to_numpy().reshape(n, self.H, self.Dv)
 
     def oracle(self, q, k, v, gate=None):
