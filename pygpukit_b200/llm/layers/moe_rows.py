@@ -1,7 +1,8 @@
 """Mixture of experts of the token-major models (net-new; beside `MoELayer`, whose router is top-k then softmax over
 the chosen logits and whose experts are FP8 / NVF4 GEMVs on bfloat16 rows).
 
-Router: float32 logits from the router GEMM (bfloat16 products are exact in float32), then pgk_moe_route_grouped:
+Router: float32 logits from the router GEMM (the router matrix is kept in float32 in both modes, so the logits are
+FMAs on the unrounded residual stream), then pgk_moe_route_grouped:
 softmax over ALL experts, optional group limit (only members of the best
 `group_keep` of `group_count` groups of neighbours), the `top` largest scores, renormalised.  Experts: stacked
 [E, 2 ff, W] gate/up pairs (SiLU * up in the GEMM epilogue) and [E, W, ff] down matrices.

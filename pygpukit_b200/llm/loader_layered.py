@@ -4,7 +4,8 @@
 `model.safetensors` next to it; `build_layered_model(config, tensors, dtype)` takes the tensors as a
 {name: float32 ndarray} dictionary (tests, random initialisation).  dtype "bfloat16": matrices go to the device as
 bfloat16 (rounded to nearest even when the file holds wider floats), cache in bfloat16; "float32": matrices and
-cache in float32.  Norm weights, biases and other small vectors are float32 on the device in both modes.
+cache in float32.  Norm weights, biases, other small vectors and the router matrices are float32 on the device in both
+modes (the router's logits are formed from the unrounded float32 residual stream).
 
 Dolurax tensor names: embed, head, final.norm(.b); per layer l<i>.norm1(.b), l<i>.norm2(.b), l<i>.mix.{q,k,v,g,o},
 l<i>.mix.{q,k}.norm, l<i>.mix.vmix (scalar), l<i>.mlp.router, l<i>.mlp.e<j>.{gate,up,down},
@@ -102,7 +103,8 @@ def build_layered_model(config: LayeredConfig, tensors, dtype: str = "bfloat16")
                 sgu = LinearRows(_matrix(interleave_gate_up(t.f32(s + "gate", (f.shared_ff, W)), t.f32(s + "up", (f.shared_ff, W))),
                                          dtype), epilogue=1)
                 sdn = LinearRows(_matrix(t.f32(s + "down", (W, f.shared_ff)), dtype))
-            mlp = GroupedRouterMoE(f, _matrix(t.f32(q + "router", (f.experts, W)), dtype),
+            # the router stays float32 in both modes: its logits come from the unrounded residual stream
+            mlp = GroupedRouterMoE(f, _matrix(t.f32(q + "router", (f.experts, W)), "float32"),
                                    LinearRows(_matrix(gu, dtype), epilogue=1), LinearRows(_matrix(dn, dtype)), sgu, sdn)
             norm2 = (_vector(t.f32(p + "norm2", (W,))), _vector(t.f32(p + "norm2.b", (W,))))
         blocks.append(PostNormBlock(mixer, norm1, mlp, norm2, eps))

@@ -322,10 +322,9 @@ def random_layered_model(config, dtype: str = "bfloat16", seed: int = 1234, std:
             f = L.mlp
             sgu = LinearRows(mat(2 * f.shared_ff, W), epilogue=1) if f.shared_ff else None
             sdn = LinearRows(mat(W, f.shared_ff)) if f.shared_ff else None
-            mlp = GroupedRouterMoE(f, mat(f.experts, W), LinearRows(mat(f.experts, 2 * f.ff, W), epilogue=1),
+            mlp = GroupedRouterMoE(f, mat(f.experts, W).astype(float32), LinearRows(mat(f.experts, 2 * f.ff, W), epilogue=1),
                                    LinearRows(mat(f.experts, W, f.ff)), sgu, sdn)
             norm2 = (vec(W, 1.0), vec(W, 0.0))
         blocks.append(PostNormBlock(mixer, (vec(W, 1.0), vec(W, 0.0)), mlp, norm2, eps))
     head = LinearRows(mat(V, W), epilogue=2, scale=config.logit_scale, cap=config.logit_softcap)
-    _ = float32
     return LayeredCausalModel(config, mat(V, W), blocks, (vec(W, 1.0), vec(W, 0.0)), head, dtype)
