@@ -514,12 +514,14 @@ int pgk_seq_mixer_prep(float* proj, int ld, int tokens, int heads, int kv_heads,
  * sigmoid(proj[row, gate_off + ...]) when gate != 0.  splits > 1 (few long tiles: decoding) cuts every tile's key range
  * into that many slices over grid.z; their partial (max, sum, P.V) records go through workspace
  * [rows][heads][splits][vdim + 2] and the block that arrives last at the tile's ticket (tickets [n_tiles x head blocks],
- * zero between launches) folds them. */
+ * zero between launches) folds them.  single_query != 0 promises one query per tile (decoding) and selects the kernel
+ * without shared-memory K/V tiles: every warp takes 32 keys at a time for up to pgk_seq_decode_heads_per_block heads. */
 int pgk_seq_attention(const float* proj, int ld, int q_off, int gate_off, float* out, int ldo, const void* k_cache,
                       const void* v_cache, int cache_dtype, const int32_t* table, int max_pages, int page_size,
                       const int32_t* tiles, int n_tiles, const float* slopes, int heads, int kv_heads, int dim, int vdim,
                       int chunk, float scale, float softcap, int gate, int splits, float* workspace, uint32_t* tickets,
-                      void* stream);
+                      int single_query, void* stream);
+int pgk_seq_decode_heads_per_block(void);
 int pgk_seq_heads_per_block(int heads, int kv_heads);
 int pgk_seq_queries_per_tile(int heads, int kv_heads);
 

@@ -90,6 +90,7 @@ __device__ __forceinline__ void stage_rows(float* dst, int ld, const TC* base, c
     constexpr int VEC = 16 / sizeof(TC);
     if (n % VEC == 0) {
         const int vpr = n / VEC;
+#pragma unroll 2
         for (int i = threadIdx.x; i < KT * vpr; i += blockDim.x) {
             const int r = i / vpr, c = (i - r * vpr) * VEC;
             float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -339,6 +340,317 @@ int launch_attn_nv(const AttnArgs& a, int tiles, cudaStream_t st) {
     return 1;
 }
 
+
+// ---------------------------------------------------------------- decoding: one query per tile
+// A tile holds ONE query; its (at most DPAIRS = 8 or 2) heads of the KV group are served by every warp.  No shared-memory K/V
+// tiles and no block barrier in the key loop: a warp takes 32 keys at a time (a lane per key, the key's row read from the
+// cache with 16-byte loads, q broadcast from shared memory), keeps its own online-softmax state for all heads, and reads
+// the V rows coalesced (a lane owns NV consecutive value columns).  The eight warps' states are folded through shared
+// memory; with key slices (grid.z) the block leaves one record per head and the last-arriving block folds the slices.
+constexpr int DPAIRS_MAX = 8;
+
+template <typename TC, int NV>
+__device__ __forceinline__ void load_values(const TC* p, bool vec, int n_left, float (&out)[NV]) {
+    if (vec) {
+        if constexpr (sizeof(TC) * NV == 16) {
+            const uint4 v = *(const uint4*)p;
+            if constexpr (sizeof(TC) == 2) {
+                out[0] = bf16lo(v.x); out[1] = bf16hi(v.x); out[2] = bf16lo(v.y); out[3] = bf16hi(v.y);
+                out[4] = bf16lo(v.z); out[5] = bf16hi(v.z); out[6] = bf16lo(v.w); out[7] = bf16hi(v.w);
+            } else {
+                out[0] = __uint_as_float(v.x); out[1] = __uint_as_float(v.y); out[2] = __uint_as_float(v.z); out[3] = __uint_as_float(v.w);
+            }
+            return;
+        } else if constexpr (sizeof(TC) * NV == 8) {
+            const uint2 v = *(const uint2*)p;
+            if constexpr (sizeof(TC) == 2) { out[0] = bf16lo(v.x); out[1] = bf16hi(v.x); out[2] = bf16lo(v.y); out[3] = bf16hi(v.y); }
+            else { out[0] = __uint_as_float(v.x); out[1] = __uint_as_float(v.y); }
+            return;
+        } else if constexpr (sizeof(TC) * NV == 4 && sizeof(TC) == 2) {
+            const uint32_t v = *(const uint32_t*)p;
+            out[0] = bf16lo(v); out[1] = bf16hi(v);
+            return;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) out[i] = i < n_left ? cload<TC>(p + i) : 0.f;
+}
+
+template <typename TC, int NV, int DPAIRS>
+__global__ void __launch_bounds__(256) seq_attention_decode_kernel(AttnArgs a) {
+    extern __shared__ __align__(16) float sm[];
+    const int D = a.D, Dv = a.Dv;
+    float* qs = sm;                                    // [DPAIRS][D]
+    float* st_m = qs + DPAIRS * D;                     // [NWARP][DPAIRS]
+    float* st_l = st_m + NWARP * DPAIRS;               // [NWARP][DPAIRS]
+    float* st_acc = st_l + NWARP * DPAIRS;             // [NWARP][DPAIRS][Dv]
+
+    const int4 tile = a.tiles[blockIdx.x];
+    const int t0 = tile.x, slot = tile.z, pos = tile.w;
+    const int rep = a.H / a.G, hsplit = (rep + DPAIRS - 1) / DPAIRS;
+    const int g = blockIdx.y / hsplit, hpart = blockIdx.y - g * hsplit;
+    const int hb0 = g * rep + hpart * DPAIRS, nh = min(DPAIRS, rep - hpart * DPAIRS);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    // loads that depend on nothing but the tile go out first: the gate values of this thread's outputs (used last) ...
+    constexpr int GPT = 4;                                // outputs (head, column) per thread kept in registers
+    float gz[GPT];
+#pragma unroll
+    for (int u = 0; u < GPT; ++u) {
+        const int i = threadIdx.x + u * 256;
+        gz[u] = (a.gate && i < nh * Dv) ? a.proj[(size_t)t0 * a.ld + a.g_off + (size_t)hb0 * Dv + i] : 0.f;
+    }
+    for (int i = threadIdx.x; i < DPAIRS * D; i += blockDim.x) {
+        const int p = i / D, d = i - p * D;
+        qs[i] = p < nh ? a.proj[(size_t)t0 * a.ld + a.q_off + (size_t)(hb0 + p) * D + d] : 0.f;
+    }
+    float slope[DPAIRS];
+#pragma unroll
+    for (int p = 0; p < DPAIRS; ++p) slope[p] = (p < nh && a.slopes) ? a.slopes[hb0 + p] : 0.f;
+    // ... and the page of the warp's first key tile
+    const int jlo = a.chunk > 0 ? (pos / a.chunk) * a.chunk : 0, jhi = pos;
+    const int ntile = (jhi - jlo) / KT + 1, per = (ntile + a.splits - 1) / a.splits;
+    const int tb = (int)blockIdx.z * per, te = min(ntile, tb + per);
+    int page_first = 0;
+    {
+        const int j = jlo + (tb + warp) * KT + lane;
+        if (tb + warp < te && j <= jhi) page_first = a.table[(size_t)slot * a.max_pages + j / a.PS];
+    }
+    __syncthreads();
+
+    float m[DPAIRS], l[DPAIRS], acc[DPAIRS][NV];
+#pragma unroll
+    for (int p = 0; p < DPAIRS; ++p) {
+        m[p] = -INFINITY; l[p] = 0.f;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) acc[p][v] = 0.f;
+    }
+    const TC* kc = (const TC*)a.kc;
+    const TC* vc = (const TC*)a.vc;
+    constexpr int KV = 16 / sizeof(TC);
+    const bool kvec = D % KV == 0, vvec = Dv % NV == 0;
+    for (int ti = tb + warp; ti < te; ti += NWARP) {
+        const int j = jlo + ti * KT + lane;
+        const bool in = j <= jhi;
+        long long ko = 0, vo = 0;
+        if (in) {
+            const int page = ti == tb + warp ? page_first : a.table[(size_t)slot * a.max_pages + j / a.PS], r = j % a.PS;
+            ko = (((long long)page * a.G + g) * a.PS + r) * D;
+            vo = (((long long)page * a.G + g) * a.PS + r) * Dv;
+        }
+        float s[DPAIRS];
+#pragma unroll
+        for (int p = 0; p < DPAIRS; ++p) s[p] = 0.f;
+        if (in) {
+            if (kvec) {
+                for (int d0 = 0; d0 < D; d0 += 4 * KV) {          // four 16-byte loads of the key's row in flight
+                    uint4 raw[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (d0 + u * KV < D) raw[u] = *(const uint4*)(kc + ko + d0 + u * KV);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int d = d0 + u * KV;
+                        if (d >= D) break;
+                        const uint4 v = raw[u];
+                        float kf[8];
+                        if (sizeof(TC) == 2) {
+                            kf[0] = bf16lo(v.x); kf[1] = bf16hi(v.x); kf[2] = bf16lo(v.y); kf[3] = bf16hi(v.y);
+                            kf[4] = bf16lo(v.z); kf[5] = bf16hi(v.z); kf[6] = bf16lo(v.w); kf[7] = bf16hi(v.w);
+                        } else {
+                            kf[0] = __uint_as_float(v.x); kf[1] = __uint_as_float(v.y); kf[2] = __uint_as_float(v.z); kf[3] = __uint_as_float(v.w);
+                        }
+#pragma unroll
+                        for (int p = 0; p < DPAIRS; ++p) {
+                            float qf[8];
+                            *(float4*)&qf[0] = *(const float4*)(qs + p * D + d);
+                            if (KV == 8) *(float4*)&qf[4] = *(const float4*)(qs + p * D + d + 4);
+#pragma unroll
+                            for (int e = 0; e < KV; ++e) s[p] = fmaf(qf[e], kf[e], s[p]);
+                        }
+                    }
+                }
+            } else {
+                for (int d = 0; d < D; ++d) {
+                    const float kv = cload<TC>(kc + ko + d);
+#pragma unroll
+                    for (int p = 0; p < DPAIRS; ++p) s[p] = fmaf(qs[p * D + d], kv, s[p]);
+                }
+            }
+        }
+        float pr[DPAIRS];
+#pragma unroll
+        for (int p = 0; p < DPAIRS; ++p) {
+            float sc = s[p] * a.scale;
+            if (a.cap > 0.f) sc = a.cap * tanhf(sc / a.cap);
+            sc -= slope[p] * (float)(pos - j);
+            sc = (in && p < nh) ? sc : -INFINITY;
+            const float mn = fmaxf(m[p], warp_max(sc));
+            if (mn == -INFINITY) { pr[p] = 0.f; continue; }
+            const float corr = expf(m[p] - mn);
+            pr[p] = expf(sc - mn);
+            l[p] = l[p] * corr + warp_sum(pr[p]);
+            m[p] = mn;
+#pragma unroll
+            for (int v = 0; v < NV; ++v) acc[p][v] *= corr;
+        }
+        const int nvalid = min(KT, jhi - (jlo + ti * KT) + 1);
+        const int dv0 = lane * NV;
+        for (int jj0 = 0; jj0 < nvalid; jj0 += 8) {                // eight V rows in flight
+            float vv[8][NV];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const long long voj = __shfl_sync(0xffffffffu, vo, (jj0 + u) & 31);
+                if (jj0 + u < nvalid && dv0 < Dv) load_values<TC, NV>(vc + voj + dv0, vvec, Dv - dv0, vv[u]);
+                else {
+#pragma unroll
+                    for (int v = 0; v < NV; ++v) vv[u][v] = 0.f;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+#pragma unroll
+                for (int p = 0; p < DPAIRS; ++p) {
+                    const float pj = __shfl_sync(0xffffffffu, pr[p], (jj0 + u) & 31);
+#pragma unroll
+                    for (int v = 0; v < NV; ++v) acc[p][v] = fmaf(jj0 + u < nvalid ? pj : 0.f, vv[u][v], acc[p][v]);
+                }
+            }
+        }
+    }
+    // fold the warps
+#pragma unroll
+    for (int p = 0; p < DPAIRS; ++p) {
+        if (lane == 0) { st_m[warp * DPAIRS + p] = m[p]; st_l[warp * DPAIRS + p] = l[p]; }
+#pragma unroll
+        for (int v = 0; v < NV; ++v)
+            if (lane * NV + v < Dv) st_acc[((size_t)warp * DPAIRS + p) * Dv + lane * NV + v] = acc[p][v];
+    }
+    __syncthreads();
+    const size_t t = t0;
+    for (int i = threadIdx.x; i < nh * Dv; i += blockDim.x) {
+        const int p = i / Dv, dv = i - p * Dv;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NWARP; ++w) M = fmaxf(M, st_m[w * DPAIRS + p]);
+        float L = 0.f, o = 0.f;
+#pragma unroll
+        for (int w = 0; w < NWARP; ++w) {
+            const float mw = st_m[w * DPAIRS + p];
+            if (mw != -INFINITY) {
+                const float e = expf(mw - M);
+                L = fmaf(st_l[w * DPAIRS + p], e, L);
+                o = fmaf(st_acc[((size_t)w * DPAIRS + p) * Dv + dv], e, o);
+            }
+        }
+        const int h = hb0 + p;
+        if (a.splits > 1) {
+            float* rec = a.ws + ((t * a.H + h) * a.splits + blockIdx.z) * (Dv + 2);
+            if (dv == 0) { rec[0] = M; rec[1] = L; }
+            rec[2 + dv] = o;
+        } else {
+            o = L > 0.f ? o / L : 0.f;
+            if (a.gate) {
+                const int u = (i - (int)threadIdx.x) >> 8;
+                float z = 0.f;
+#pragma unroll
+                for (int uu = 0; uu < GPT; ++uu)
+                    if (uu == u) z = gz[uu];
+                if (u >= GPT) z = a.proj[t * a.ld + a.g_off + (size_t)h * Dv + dv];
+                o *= 1.f / (1.f + expf(-z));
+            }
+            a.out[t * a.ldo + (size_t)h * Dv + dv] = o;
+        }
+    }
+    if (a.splits == 1) return;
+    __shared__ unsigned last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned* tk = a.tickets + (size_t)blockIdx.x * gridDim.y + blockIdx.y;
+        const unsigned n = atomicAdd(tk, 1u);
+        last = (n == (unsigned)a.splits - 1u);
+        if (last) *tk = 0u;
+    }
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    __shared__ float wsl[DPAIRS][64];
+    if (warp < nh) {                                   // weights of the slices: one warp per head, lanes over slices
+        const float* rec = a.ws + ((t * a.H + hb0 + warp) * a.splits) * (Dv + 2);
+        float ms[2], ls[2], M = -INFINITY;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int sp = lane + 32 * u;
+            ms[u] = sp < a.splits ? __ldcg(rec + (size_t)sp * (Dv + 2)) : -INFINITY;
+            ls[u] = sp < a.splits ? __ldcg(rec + (size_t)sp * (Dv + 2) + 1) : 0.f;
+            M = fmaxf(M, ms[u]);
+        }
+        M = warp_max(M);
+        float e[2], L = 0.f;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) { e[u] = ms[u] == -INFINITY ? 0.f : expf(ms[u] - M); L += ls[u] * e[u]; }
+        L = warp_sum(L);
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+            if (lane + 32 * u < a.splits) wsl[warp][lane + 32 * u] = e[u] * inv;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < nh * Dv; i += blockDim.x) {
+        const int p = i / Dv, dv = i - p * Dv, h = hb0 + p;
+        const float* rec = a.ws + ((t * a.H + h) * a.splits) * (Dv + 2) + 2 + dv;
+        float o = 0.f;
+#pragma unroll 8
+        for (int sp = 0; sp < a.splits; ++sp) o = fmaf(wsl[p][sp], __ldcg(rec + (size_t)sp * (Dv + 2)), o);
+        if (a.gate) {
+            const int u = (i - (int)threadIdx.x) >> 8;
+            float z = 0.f;
+#pragma unroll
+            for (int uu = 0; uu < GPT; ++uu)
+                if (uu == u) z = gz[uu];
+            if (u >= GPT) z = a.proj[t * a.ld + a.g_off + (size_t)h * Dv + dv];
+            o *= 1.f / (1.f + expf(-z));
+        }
+        a.out[t * a.ldo + (size_t)h * Dv + dv] = o;
+    }
+}
+
+template <typename TC, int NV, int DPAIRS>
+int launch_attn_decode_dp(const AttnArgs& a, int tiles, cudaStream_t st) {
+    const size_t smem = sizeof(float) * ((size_t)DPAIRS * a.D + 2 * NWARP * DPAIRS + (size_t)NWARP * DPAIRS * a.Dv);
+    PGK_REQUIRE(smem <= 200 * 1024, "seq_attention failed: head sizes %d / %d need %zu bytes of shared memory", a.D, a.Dv, smem);
+    static bool configured = false;
+    if (smem > 48 * 1024 && !configured) {
+        PGK_CUDA(cudaFuncSetAttribute(seq_attention_decode_kernel<TC, NV, DPAIRS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        configured = true;
+    }
+    const int rep = a.H / a.G, hsplit = (rep + DPAIRS - 1) / DPAIRS;
+    PGK_CUDA(launch(seq_attention_decode_kernel<TC, NV, DPAIRS>, dim3(tiles, a.G * hsplit, a.splits), dim3(256), smem, st, a));
+    return 0;
+}
+
+// Few blocks (one or a handful of requests): two heads per block instead of eight -- four times the blocks, a quarter of
+// the instructions on each warp's critical path; the K/V rows are then read four times, from L2.
+template <typename TC, int NV>
+int launch_attn_decode(const AttnArgs& a, int tiles, cudaStream_t st) {
+    const int rep = a.H / a.G;
+    const long long blocks8 = (long long)tiles * a.G * ((rep + DPAIRS_MAX - 1) / DPAIRS_MAX) * a.splits;
+    if (rep > 2 && blocks8 * 4 <= 2 * 148) return launch_attn_decode_dp<TC, NV, 2>(a, tiles, st);
+    return launch_attn_decode_dp<TC, NV, DPAIRS_MAX>(a, tiles, st);
+}
+
+template <typename TC>
+int launch_attn_decode_nv(const AttnArgs& a, int tiles, cudaStream_t st) {
+    const int nv = (a.Dv + 31) / 32;
+    if (nv <= 1) return launch_attn_decode<TC, 1>(a, tiles, st);
+    if (nv <= 2) return launch_attn_decode<TC, 2>(a, tiles, st);
+    if (nv <= 4) return launch_attn_decode<TC, 4>(a, tiles, st);
+    if (nv <= 8) return launch_attn_decode<TC, 8>(a, tiles, st);
+    set_error("seq_attention failed: value size %d exceeds 256", a.Dv);
+    return 1;
+}
+
 }  // namespace
 
 extern "C" {
@@ -368,7 +680,7 @@ int pgk_seq_attention(const float* proj, int ld, int q_off, int gate_off, float*
                       const void* v_cache, int cache_dtype, const int32_t* table, int max_pages, int page_size,
                       const int32_t* tiles, int n_tiles, const float* slopes, int heads, int kv_heads, int dim, int vdim,
                       int chunk, float scale, float softcap, int gate, int splits, float* workspace, uint32_t* tickets,
-                      void* stream) {
+                      int single_query, void* stream) {
     PGK_REQUIRE(cache_dtype == 0 || cache_dtype == 2, "seq_attention failed: the cache is float32 (0) or bfloat16 (2), got %d", cache_dtype);
     PGK_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0, "seq_attention failed: invalid head layout");
     PGK_REQUIRE(splits >= 1 && splits <= 64 && (splits == 1 || (workspace && tickets)),
@@ -377,8 +689,12 @@ int pgk_seq_attention(const float* proj, int ld, int q_off, int gate_off, float*
     AttnArgs a{proj, ld, q_off, gate_off, out, ldo, k_cache, v_cache, table, max_pages, page_size, (const int4*)tiles, slopes,
                heads, kv_heads, dim, vdim, chunk, pgk_seq_heads_per_block(heads, kv_heads), gate, scale, softcap, splits, workspace,
                tickets};
+    if (single_query)       // every tile holds one query: the decoding kernel
+        return cache_dtype == 2 ? launch_attn_decode_nv<uint16_t>(a, n_tiles, (cudaStream_t)stream)
+                                : launch_attn_decode_nv<float>(a, n_tiles, (cudaStream_t)stream);
     return cache_dtype == 2 ? launch_attn_nv<uint16_t>(a, n_tiles, (cudaStream_t)stream)
                             : launch_attn_nv<float>(a, n_tiles, (cudaStream_t)stream);
 }
+int pgk_seq_decode_heads_per_block(void) { return DPAIRS_MAX; }
 
 }  // extern "C"

@@ -36,6 +36,7 @@ class PagedAttentionMixer:
         self.slopes = from_numpy(np.asarray(sl, np.float32)) if sl else None
         self.queries_per_tile = int(api.seq_queries_per_tile(s.heads, s.kv_heads))
         self.heads_per_block = int(api.seq_heads_per_block(s.heads, s.kv_heads))
+        self.decode_heads_per_block = int(api.seq_decode_heads_per_block())
 
     @property
     def weight_bytes(self) -> int:
@@ -46,11 +47,16 @@ class PagedAttentionMixer:
         the whole GPU reads the cache.  A power of two, so that a decode step's launch shapes change rarely."""
         s = self.spec
         n_tiles = ctx.tiles(self.queries_per_tile)[1]
-        blocks = n_tiles * s.kv_heads * -(-(s.heads // s.kv_heads) // self.heads_per_block)
+        rep = s.heads // s.kv_heads
         keys = ctx.max_keys(s.chunk)
-        if blocks >= 148 or keys < 256:
-            return 1
-        want = max(1, min(64, -(-keys // 32), 592 // blocks))
+        if ctx.decode_only:          # the decoding kernel: eight warps take 32 keys each per round
+            blocks = n_tiles * s.kv_heads * -(-rep // self.decode_heads_per_block)
+            want = max(1, min(64, -(-keys // 256), 592 // max(1, blocks)))
+        else:
+            blocks = n_tiles * s.kv_heads * -(-rep // self.heads_per_block)
+            if blocks >= 148 or keys < 256:
+                return 1
+            want = max(1, min(64, -(-keys // 32), 592 // blocks))
         return min(64, 1 << (want - 1).bit_length())
 
     def forward(self, ctx, x: GPUArray, out: GPUArray) -> None:
@@ -77,7 +83,7 @@ class PagedAttentionMixer:
                           kc.device_ptr, vc.device_ptr, cache.dtype_code, cache.table_dev.device_ptr, cache.pool.max_pages,
                           cache.page_size, tiles_ptr, n_tiles, self.slopes.device_ptr if self.slopes is not None else None,
                           s.heads, s.kv_heads, s.dim, s.vdim, s.chunk, s.scale, s.softcap, 1 if s.out_gate else 0,
-                          splits, ws, tickets, _st())
+                          splits, ws, tickets, 1 if ctx.decode_only else 0, _st())
         self.o_proj.forward(attn.device_ptr, ldo, T, out.device_ptr, self.o_proj.out_features)
 
 

@@ -179,6 +179,7 @@ class AttnHarness:
 
     def __init__(self, H, G, D, Dv, chunk, scale=0.3, softcap=0.0, page=4, dtype="float32", gate=False, splits=1):
         self.splits = splits
+        self.decode_kernel = True          # one-token calls go through the decoding kernel
         self.H, self.G, self.D, self.Dv, self.chunk, self.scale, self.softcap, self.gate = H, G, D, Dv, chunk, scale, softcap, gate
         self.cache = PagedKVCache([(G, D, Dv)], dtype, page, 64, 2)
         self.qt = api.seq_queries_per_tile(H, G)
@@ -206,7 +207,7 @@ class AttnHarness:
                           c.pool.max_pages, c.page_size, i32(tiles).device_ptr, len(tiles), self.slopes.device_ptr, self.H,
                           self.G, self.D, self.Dv, self.chunk, self.scale, self.softcap, 1 if self.gate else 0, self.splits,
                           keep(gk.zeros((n * self.H * self.splits * (self.Dv + 2),), gk.float32)).device_ptr,
-                          self.tickets.device_ptr, None)
+                          self.tickets.device_ptr, 1 if (n == 1 and self.decode_kernel) else 0, None)
         assert not self.tickets.to_numpy().any()                         # the tickets clear themselves
         return out.to_numpy().reshape(n, self.H, self.Dv)
 
@@ -233,6 +234,10 @@ def test_attention_whole_portions_and_single_tokens_agree_with_the_oracle(H, G, 
     assert np.abs(parts - ref).max() < 1e-5
     h.cache.release("w")                                                 # its pages serve the next sequence
     single = np.concatenate([h.run("s", q[i:i + 1], k[i:i + 1], v[i:i + 1], gate[i:i + 1]) for i in range(T)])
+    assert np.abs(single - ref).max() < 1e-5
+    h.cache.release("p")
+    h.decode_kernel = False                                              # the same through the tile kernel
+    single = np.concatenate([h.run("t", q[i:i + 1], k[i:i + 1], v[i:i + 1], gate[i:i + 1]) for i in range(T)])
     assert np.abs(single - ref).max() < 1e-5
 
 
