@@ -119,7 +119,7 @@ def test_gemm_grouped_and_per_row(wdt):
     assert np.abs(c2.to_numpy() - ref2).max() < 1e-4
 
 
-@pytest.mark.parametrize("E,top,gc,keep", [(16, 4, 2, 1), (16, 3, 4, 2), (8, 2, 1, 1), (12, 1, 3, 3), (6, 6, 2, 2), (40, 5, 5, 2)])
+@pytest.mark.parametrize("E,top,gc,keep", [(16, 4, 2, 1), (16, 3, 4, 2), (8, 2, 1, 1), (12, 1, 3, 3), (6, 6, 2, 2), (40, 5, 5, 2), (64, 40, 1, 1)])
 @pytest.mark.parametrize("wdt", [0, 2])
 def test_router_and_row_lists(E, top, gc, keep, wdt):
     rng = np.random.default_rng(E + top)
