@@ -49,6 +49,11 @@ __device__ __forceinline__ void store_pair(const GemmArgs& a, int row, int col, 
 
 constexpr int BM = 64, BN = 64, BK = 32;
 
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(smem_row)));
+}
+
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -140,20 +145,16 @@ __global__ void __launch_bounds__(128) gemm_rows_bf16_kernel(GemmArgs a) {
         if (kt + 1 < nk) fetch((kt + 1) * BK);
 #pragma unroll
         for (int kk = 0; kk < BK; kk += 16) {
+            // fragments by ldmatrix (rows are 80 bytes apart: 16-byte aligned and conflict-free)
             uint32_t af[2][4], bf[4][2];
 #pragma unroll
-            for (int mi = 0; mi < 2; ++mi) {
-                const int r = wm * 32 + mi * 16 + g;
-                af[mi][0] = *(const uint32_t*)&As[buf][r][kk + 2 * tg];
-                af[mi][1] = *(const uint32_t*)&As[buf][r + 8][kk + 2 * tg];
-                af[mi][2] = *(const uint32_t*)&As[buf][r][kk + 2 * tg + 8];
-                af[mi][3] = *(const uint32_t*)&As[buf][r + 8][kk + 2 * tg + 8];
-            }
+            for (int mi = 0; mi < 2; ++mi)      // 16 x 16 of A: lanes 0-15 name rows 0-15 at k, lanes 16-31 the same rows at k + 8
+                ldmatrix_x4(af[mi], &As[buf][wm * 32 + mi * 16 + (lane & 15)][kk + ((lane >> 4) << 3)]);
 #pragma unroll
-            for (int ni = 0; ni < 4; ++ni) {
-                const int c = wn * 32 + ni * 8 + g;
-                bf[ni][0] = *(const uint32_t*)&Ws[buf][c][kk + 2 * tg];
-                bf[ni][1] = *(const uint32_t*)&Ws[buf][c][kk + 2 * tg + 8];
+            for (int nj = 0; nj < 2; ++nj) {    // 16 columns x 16 k of W: (n 0-7, k 0-7), (n 0-7, k 8-15), (n 8-15, k 0-7), (n 8-15, k 8-15)
+                uint32_t r[4];
+                ldmatrix_x4(r, &Ws[buf][wn * 32 + nj * 16 + (lane & 7) + ((lane >> 4) << 3)][kk + (((lane >> 3) & 1) << 3)]);
+                bf[2 * nj][0] = r[0]; bf[2 * nj][1] = r[1]; bf[2 * nj + 1][0] = r[2]; bf[2 * nj + 1][1] = r[3];
             }
 #pragma unroll
             for (int mi = 0; mi < 2; ++mi)

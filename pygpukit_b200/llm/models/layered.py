@@ -178,6 +178,10 @@ class LayeredCausalModel:
         if self.cache is None:
             self.init_cache()
         V = self.config.vocab_size
+        if not entries:                                # nothing to run: only give back what `end` names
+            for seq_id in end:
+                self.cache.release(seq_id)
+            return None, 0
         ctx = StepContext(self, entries, self._tile_sizes, self._tops)
         if self._out is None or self._out.shape[0] < max(ctx.n_want, 1):
             self._out = GPUArray((max(ctx.n_want, 16), V), float32)
