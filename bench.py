@@ -31,6 +31,10 @@ the step's HBM roofline fraction): Llama-3-8B FP8 @4k (north_star's >= 70 % targ
   --impl reference   the CPU arm: K + W real steps, each `layers_per_step` decoder layers + the matching share of
           the lm_head, so that the K timed steps are whole tokens' worth of work; nothing is extrapolated.
 N > 1 (torchrun): tensor-parallel over N GPUs (strong scaling: the same token stream, weights sharded).
+
+    python bench.py --layered [--layered-sizes a3b-2048,moe-4096] [--steps K] [--warmup W]
+An option beside the default workload (whose contract is unchanged): prompt and decode throughput of the layered
+(Dolurax) family at real layer sizes next to Qwen3-MoE at equal sizes, one JSON line (scripts/bench_layered.py).
 """
 from __future__ import annotations
 
