@@ -471,7 +471,7 @@ int pgk_p2p_destroy(void);
  * net-new: no counterpart in the reference (its models run one sequence on a fixed cache in 16 bits).  Rows are the
  * tokens of a step -- any mix of prompt portions and single decoded tokens of different sequences -- and every
  * activation is float32; weight matrices are [N, K] in float32 (dtype code 0) or bfloat16 (2).  seq_gemm.cu,
- * seq_attention.cu, seq_layers.cu. */
+ * seq_attention.cu, seq_layers.cu, seq_latent.cu. */
 /* C[m, :] = A[a_rows ? a_rows[m] : m, :] . W[g]^T.  group_off [groups + 1] (or NULL) cuts rows 0 .. group_off[groups] into
  * consecutive runs, run g uses matrix W + g * w_group_stride (max_rows bounds the longest run).  epilogue 0: plain;
  * 1: W rows are (gate_j, up_j) pairs, C[m, j] = silu(gate) * up, ldc >= N / 2; 2: c * scale, then cap * tanh(c / cap)
@@ -521,6 +521,51 @@ int pgk_seq_attention(const float* proj, int ld, int q_off, int gate_off, float*
                       const int32_t* tiles, int n_tiles, const float* slopes, int heads, int kv_heads, int dim, int vdim,
                       int chunk, float scale, float softcap, int gate, int splits, float* workspace, uint32_t* tickets,
                       int single_query, void* stream);
+/* pgk_seq_attention with its optional parts named: the query rows (row stride ldq, head h at q_off + h * dim) and the rows
+ * the gate is read from are separate arrays; gate_mode 0 none, 1 sigmoid(gate_rows[row, gate_off + h * vdim + c]) per output
+ * element, 2 sigmoid(gate_rows[row, gate_off + h]) per head; sinks [heads] (or NULL): a score per head that enters the softmax
+ * denominator once, unscaled, and has no value; window > 0: key j is visible from i only when i - j < window; k_ld / v_ld:
+ * elements between the rows of consecutive positions in the cache arrays (v_cache == k_cache with v_ld == k_ld: the values
+ * are the first vdim elements of the key rows -- latent attention). */
+int pgk_seq_attention_ex(const float* q, int ldq, int q_off, const float* gate_rows, int ldg, int gate_off, int gate_mode,
+                         float* out, int ldo, const void* k_cache, const void* v_cache, int k_ld, int v_ld, int cache_dtype,
+                         const int32_t* table, int max_pages, int page_size, const int32_t* tiles, int n_tiles,
+                         const float* slopes, const float* sinks, int heads, int kv_heads, int dim, int vdim, int chunk,
+                         int window, float scale, float softcap, int splits, float* workspace, uint32_t* tickets,
+                         int single_query, void* stream);
+/* mixer_prep for layers whose q / k norm runs over the WHOLE projection: per token, q <- (q + q_bias) / rms(all heads x dim
+ * of q) * (weight_offset + q_weight) in place (proj[t, 0 ..]), k the same from proj[t, k_off ..] with k_weight into the K
+ * pages; the V pages receive k + k_bias as projected (before the norm).  Biases may be NULL; weights are [heads x dim] and
+ * [kv_heads x dim]. */
+int pgk_seq_mixer_prep_all(float* proj, int ld, int tokens, int heads, int kv_heads, int dim, int k_off, const float* q_bias,
+                           const float* k_bias, const float* q_weight, const float* k_weight, float weight_offset, float eps,
+                           void* k_cache, void* v_cache, int cache_dtype, const int32_t* table, int max_pages, int page_size,
+                           const int32_t* slot, const int32_t* pos, void* stream);
+/* Latent attention (seq_latent.cu).  The cache row of a position is [c (rank) | r (rot)], one "key head" of size rank + rot.
+ * latent_prep, per token on the fused projection row: proj[t, 0 .. q_rank) <- RMS norm * (weight_offset + q_weight) in place
+ * (q_rank 0: no query latent); c = RMS norm of proj[t, kv_off .. kv_off + rank) * (weight_offset + c_weight); r = the next
+ * `rot` elements, the first rot_dims of them rotated by the token's position (pairs (2i, 2i + 1), angle = position *
+ * inv_freq[i], inv_freq [rot_dims / 2] doubles on the device).
+ * rope_heads: dst[t, h * dst_head + dst_off + (0 .. rot)) = the same rotation of src[t, h * src_head + src_off + (0 .. rot)). */
+int pgk_seq_latent_prep(float* proj, int ld, int tokens, int q_rank, int kv_off, int rank, int rot, int rot_dims,
+                        const float* q_weight, const float* c_weight, float weight_offset, float eps, const double* inv_freq,
+                        void* k_cache, int cache_dtype, const int32_t* table, int max_pages, int page_size,
+                        const int32_t* slot, const int32_t* pos, void* stream);
+int pgk_seq_rope_heads(const float* src, int lds, int src_head, int src_off, float* dst, int ldd, int dst_head, int dst_off,
+                       int tokens, int heads, int rot, int rot_dims, const double* inv_freq, const int32_t* pos, void* stream);
+/* v = x[src_rows ? src_rows[t] : t] + (add ? add[t] : 0); sum_out[t] = v when given (no gather then); r = v / sqrt(mean(v^2)
+ * + eps) * (weight_offset + weight); accumulate != 0: out[t] += r, else out[t] = r.  out may be x. */
+int pgk_rms_norm_rows_f32(const float* x, const int32_t* src_rows, const float* add, float* sum_out, const float* weight,
+                          float weight_offset, float eps, float* out, int rows, int width, int accumulate, void* stream);
+/* The general row GEMM: `batch` products over the same M rows, product b reading A columns from b * a_batch, matrix
+ * W + b * w_batch and writing C columns from b * c_batch (one product per attention head).  Epilogues 0-2 as above with
+ * p0 = scale, p1 = cap; 3: gate/up pairs, g = min(gate, p1), u = clamp(up, -p1, p1), C[m, j] = g sigmoid(p0 g) (u + 1);
+ * 4: C[m, n] += col_scale[n] * product; 5: C[m, n] = gelu_tanh(product) * aux[aux_rows[m], aux_off + n] (aux float32 = 0 or
+ * bfloat16 = 2, row stride aux_ld).  rows_per_block > 0: the few-row kernel (M rows in blocks of at most 8), 0: tiles. */
+int pgk_gemm_seq_f32(const float* A, int lda, long long a_batch, const void* W, int wdt, long long w_batch, float* C, int ldc,
+                     long long c_batch, int M, int N, int K, int batch, int epilogue, float p0, float p1, const float* col_scale,
+                     const void* aux, int aux_dtype, const int32_t* aux_rows, int aux_ld, int aux_off, int rows_per_block,
+                     void* stream);
 int pgk_seq_decode_heads_per_block(void);
 int pgk_seq_heads_per_block(int heads, int kv_heads);
 int pgk_seq_queries_per_tile(int heads, int kv_heads);

@@ -50,13 +50,14 @@ SOURCES = {
     "seq_gemm.cu": [],
     "seq_attention.cu": [],
     "seq_layers.cu": [],
+    "seq_latent.cu": [],
 }
 
 # groups of sources that link on their own (runtime.cu is in every library)
 COMPONENTS = {
     "core": ["runtime.cu"],
     # token-major float32-activation models on the paged cache (llm/models/layered.py)
-    "seq": ["runtime.cu", "seq_gemm.cu", "seq_attention.cu", "seq_layers.cu"],
+    "seq": ["runtime.cu", "seq_gemm.cu", "seq_attention.cu", "seq_layers.cu", "seq_latent.cu"],
 }
 
 

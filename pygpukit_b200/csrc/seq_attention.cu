@@ -11,6 +11,12 @@
 //                j <= i and, with a chunk size C, floor(j / C) == floor(i / C); online softmax; P.V; optional output gate
 //                out *= sigmoid(gate).  A block serves one tile of consecutive queries of one sequence and one KV head
 //                (all query heads of its group), K/V tiles of 32 positions staged in shared memory, a lane per key.
+//                Optional: a sliding window (key j visible when i - j < window), a sink per head (a score that enters the
+//                softmax denominator once and has no value: the running (max, sum) starts at (sink, 1) instead of
+//                (-inf, 0)), a gate of one number per head, values that are a prefix of the key rows (latent attention:
+//                one cache array, no second staging), and row strides of the cache rows.
+//   mixer_prep_all: the form whose q / k norm runs over the WHOLE projection (all heads at once), with projection
+//                biases and values that are the keys before the norm.
 #include "common.cuh"
 #include "../../include/pgk_b200.h"
 
@@ -69,10 +75,70 @@ __global__ void __launch_bounds__(128) mixer_prep_kernel(PrepArgs a) {
     }
 }
 
+struct PrepAllArgs {
+    float* proj; int ld;
+    int H, G, D, k_off;
+    const float* qb; const float* kb; const float* qw; const float* kw; float w_off, eps;
+    void* kc; void* vc; const int* table; int max_pages, PS;
+    const int* slot; const int* pos;
+};
+
+__device__ __forceinline__ float block_sum_256(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += red[i];
+    return s;
+}
+
+// one block per token: q <- (q + b_q) / rms(all of q) * (w_off + w_q) in place; the cache gets (k + b_k) as the VALUE row and
+// (k + b_k) / rms(all of k) * (w_off + w_k) as the KEY row, head by head
+template <typename TC>
+__global__ void __launch_bounds__(256) mixer_prep_all_kernel(PrepAllArgs a) {
+    __shared__ float red[8];
+    const int t = blockIdx.x;
+    float* q = a.proj + (size_t)t * a.ld;
+    float* k = q + a.k_off;
+    const int nq = a.H * a.D, nk = a.G * a.D;
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) {
+        const float v = q[i] + (a.qb ? a.qb[i] : 0.f);
+        q[i] = v;
+        sq = fmaf(v, v, sq);
+    }
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+        const float v = k[i] + (a.kb ? a.kb[i] : 0.f);
+        k[i] = v;
+        sk = fmaf(v, v, sk);
+    }
+    sq = block_sum_256(sq, red);
+    sk = block_sum_256(sk, red);
+    const float iq = 1.f / sqrtf(sq / (float)nq + a.eps), ik = 1.f / sqrtf(sk / (float)nk + a.eps);
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) q[i] = q[i] * iq * (a.w_off + a.qw[i]);
+    const int pos = a.pos[t], slot = a.slot[t];
+    const int page = a.table[(size_t)slot * a.max_pages + pos / a.PS], r = pos % a.PS;
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+        const int g = i / a.D, d = i - g * a.D;
+        const size_t o = (((size_t)page * a.G + g) * a.PS + r) * a.D + d;
+        const float v = k[i];
+        cstore<TC>((TC*)a.vc + o, v);
+        cstore<TC>((TC*)a.kc + o, v * ik * (a.w_off + a.kw[i]));
+    }
+}
+
 struct AttnArgs {
     const float* proj; int ld, q_off, g_off;
     float* out; int ldo;
     const void* kc; const void* vc; const int* table; int max_pages, PS;
+    const float* gsrc; int ldg;         // rows the gate is read from (gate 1: g_off + h * Dv + dv, gate 2: g_off + h)
+    const float* sinks;                 // [H] or NULL: a score per head that joins the denominator and has no value
+    int window;                         // > 0: key j is visible from i only when i - j < window
+    int kld, vld;                       // elements between consecutive positions' rows in the K / V arrays
+    int valias;                         // the value rows are the first Dv elements of the key rows (one staging)
     const int4* tiles;                  // (first token row, queries, slot, first position)
     const float* slopes;                // [H] or NULL
     int H, G, D, Dv, chunk, HB, gate;
@@ -83,12 +149,21 @@ struct AttnArgs {
 
 constexpr int KT = 32;                  // keys per tile = one per lane
 
+__device__ __forceinline__ float gate_logit(const AttnArgs& a, size_t t, int h, int dv) {
+    return a.gsrc[t * a.ldg + a.g_off + (a.gate == 2 ? (size_t)h : (size_t)h * a.Dv + dv)];
+}
+__device__ __forceinline__ int first_key(const AttnArgs& a, int pos) {
+    int lo = a.chunk > 0 ? (pos / a.chunk) * a.chunk : 0;
+    if (a.window > 0) lo = max(lo, pos - a.window + 1);
+    return lo;
+}
+
 // KT cache rows of n elements -> shared memory as float32 (row stride ld), 16 bytes per load when the rows allow it;
 // rows with offset < 0 (past the last key) are zero-filled
 template <typename TC>
-__device__ __forceinline__ void stage_rows(float* dst, int ld, const TC* base, const long long* row_off, int n) {
+__device__ __forceinline__ void stage_rows(float* dst, int ld, const TC* base, const long long* row_off, int n, int src_ld) {
     constexpr int VEC = 16 / sizeof(TC);
-    if (n % VEC == 0) {
+    if (n % VEC == 0 && src_ld % VEC == 0) {
         const int vpr = n / VEC;
 #pragma unroll 2
         for (int i = threadIdx.x; i < KT * vpr; i += blockDim.x) {
@@ -122,7 +197,8 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
     const int D = a.D, Dv = a.Dv, DP = D + 1;
     float* qs = sm;                                   // [NWARP][D][PPW]
     float* Ks = qs + NWARP * D * PPW;                 // [KT][D + 1]
-    float* Vs = Ks + KT * DP;                         // [KT][Dv]
+    float* Vs = a.valias ? Ks : Ks + KT * DP;         // [KT][Dv] (the key rows themselves when the values alias them)
+    const int vstr = a.valias ? DP : Dv;
     __shared__ long long krow[KT], vrow[KT];
 
     const int4 tile = a.tiles[blockIdx.x];
@@ -144,7 +220,7 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
         ok[c] = qi[c] < nq && hh < nh;
         hd[c] = hb0 + hh;
         pi[c] = pos0 + qi[c];
-        lo[c] = a.chunk > 0 ? (pi[c] / a.chunk) * a.chunk : 0;
+        lo[c] = first_key(a, pi[c]);
         slope[c] = (ok[c] && a.slopes) ? a.slopes[hd[c]] : 0.f;
     }
     const bool warp_live = ok[0] || ok[1] || ok[2] || ok[3];
@@ -160,10 +236,11 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
 #pragma unroll
     for (int c = 0; c < PPW; ++c) {
         m[c] = -INFINITY; l[c] = 0.f;
+        if (a.sinks && ok[c] && blockIdx.z == 0) { m[c] = a.sinks[hd[c]]; l[c] = 1.f; }    // the sink counts once: slice 0
 #pragma unroll
         for (int v = 0; v < NV; ++v) acc[c][v] = 0.f;
     }
-    const int jlo = a.chunk > 0 ? (pos0 / a.chunk) * a.chunk : 0, jhi = pos0 + nq - 1;
+    const int jlo = first_key(a, pos0), jhi = pos0 + nq - 1;
     const TC* kc = (const TC*)a.kc;
     const TC* vc = (const TC*)a.vc;
     // this block's slice of the key tiles (all of them when splits == 1)
@@ -177,14 +254,14 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
             long long ko = -1, vo = -1;
             if (j <= jhi) {
                 const int page = a.table[(size_t)slot * a.max_pages + j / a.PS], r = j % a.PS;
-                ko = (((long long)page * a.G + g) * a.PS + r) * D;
-                vo = (((long long)page * a.G + g) * a.PS + r) * Dv;
+                ko = (((long long)page * a.G + g) * a.PS + r) * a.kld;
+                vo = (((long long)page * a.G + g) * a.PS + r) * a.vld;
             }
             krow[threadIdx.x] = ko; vrow[threadIdx.x] = vo;
         }
         __syncthreads();
-        stage_rows<TC>(Ks, DP, kc, krow, D);
-        stage_rows<TC>(Vs, Dv, vc, vrow, Dv);
+        stage_rows<TC>(Ks, DP, kc, krow, D, a.kld);
+        if (!a.valias) stage_rows<TC>(Vs, Dv, vc, vrow, Dv, a.vld);
         __syncthreads();
         if (!warp_live) continue;                   // a warp without a (query, head) pair only helps staging
         // scores: lane = key
@@ -223,7 +300,7 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
 #pragma unroll
             for (int v = 0; v < NV; ++v) {
                 const int dv = lane + 32 * v;
-                const float vv = dv < Dv ? Vs[jj * Dv + dv] : 0.f;
+                const float vv = dv < Dv ? Vs[jj * vstr + dv] : 0.f;
 #pragma unroll
                 for (int c = 0; c < PPW; ++c) acc[c][v] = fmaf(pj[c], vv, acc[c][v]);
             }
@@ -288,10 +365,7 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
             float o = 0.f;
 #pragma unroll 8
             for (int sp = 0; sp < a.splits; ++sp) o = fmaf(wsl[p][sp], __ldcg(rec + (size_t)sp * (Dv + 2)), o);
-            if (a.gate) {
-                const float z = a.proj[t * a.ld + a.g_off + (size_t)h * Dv + dv];
-                o *= 1.f / (1.f + expf(-z));
-            }
+            if (a.gate) o *= 1.f / (1.f + expf(-gate_logit(a, t, h, dv)));
             a.out[t * a.ldo + (size_t)h * Dv + dv] = o;
         }
         return;
@@ -306,10 +380,7 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
             const int dv = lane + 32 * v;
             if (dv >= Dv) continue;
             float o = acc[c][v] * inv;
-            if (a.gate) {
-                const float z = a.proj[t * a.ld + a.g_off + (size_t)hd[c] * Dv + dv];
-                o *= 1.f / (1.f + expf(-z));
-            }
+            if (a.gate) o *= 1.f / (1.f + expf(-gate_logit(a, t, hd[c], dv)));
             a.out[t * a.ldo + (size_t)hd[c] * Dv + dv] = o;
         }
     }
@@ -317,7 +388,7 @@ __global__ void __launch_bounds__(256) seq_attention_kernel(AttnArgs a) {
 
 template <typename TC, int NV>
 int launch_attn(const AttnArgs& a, int tiles, cudaStream_t st) {
-    const size_t smem = sizeof(float) * ((size_t)NWARP * a.D * PPW + (size_t)KT * (a.D + 1) + (size_t)KT * a.Dv);
+    const size_t smem = sizeof(float) * ((size_t)NWARP * a.D * PPW + (size_t)KT * (a.D + 1) + (a.valias ? 0 : (size_t)KT * a.Dv));
     PGK_REQUIRE(smem <= 200 * 1024, "seq_attention failed: head sizes %d / %d need %zu bytes of shared memory", a.D, a.Dv, smem);
     static size_t configured = 0;
     if (smem > 48 * 1024 && configured == 0) {
@@ -336,7 +407,8 @@ int launch_attn_nv(const AttnArgs& a, int tiles, cudaStream_t st) {
     if (nv <= 2) return launch_attn<TC, 2>(a, tiles, st);
     if (nv <= 4) return launch_attn<TC, 4>(a, tiles, st);
     if (nv <= 8) return launch_attn<TC, 8>(a, tiles, st);
-    set_error("seq_attention failed: value size %d exceeds 256", a.Dv);
+    if (nv <= 16) return launch_attn<TC, 16>(a, tiles, st);
+    set_error("seq_attention failed: value size %d exceeds 512", a.Dv);
     return 1;
 }
 
@@ -352,7 +424,21 @@ constexpr int DPAIRS_MAX = 8;
 template <typename TC, int NV>
 __device__ __forceinline__ void load_values(const TC* p, bool vec, int n_left, float (&out)[NV]) {
     if (vec) {
-        if constexpr (sizeof(TC) * NV == 16) {
+        if constexpr (sizeof(TC) * NV > 16) {
+            constexpr int PER = 16 / sizeof(TC);
+#pragma unroll
+            for (int i = 0; i < NV / PER; ++i) {
+                const uint4 v = *(const uint4*)(p + i * PER);
+                float* o = out + i * PER;
+                if constexpr (sizeof(TC) == 2) {
+                    o[0] = bf16lo(v.x); o[1] = bf16hi(v.x); o[2] = bf16lo(v.y); o[3] = bf16hi(v.y);
+                    o[4] = bf16lo(v.z); o[5] = bf16hi(v.z); o[6] = bf16lo(v.w); o[7] = bf16hi(v.w);
+                } else {
+                    o[0] = __uint_as_float(v.x); o[1] = __uint_as_float(v.y); o[2] = __uint_as_float(v.z); o[3] = __uint_as_float(v.w);
+                }
+            }
+            return;
+        } else if constexpr (sizeof(TC) * NV == 16) {
             const uint4 v = *(const uint4*)p;
             if constexpr (sizeof(TC) == 2) {
                 out[0] = bf16lo(v.x); out[1] = bf16hi(v.x); out[2] = bf16lo(v.y); out[3] = bf16hi(v.y);
@@ -398,7 +484,7 @@ __global__ void __launch_bounds__(256) seq_attention_decode_kernel(AttnArgs a) {
 #pragma unroll
     for (int u = 0; u < GPT; ++u) {
         const int i = threadIdx.x + u * 256;
-        gz[u] = (a.gate && i < nh * Dv) ? a.proj[(size_t)t0 * a.ld + a.g_off + (size_t)hb0 * Dv + i] : 0.f;
+        gz[u] = (a.gate && i < nh * Dv) ? gate_logit(a, (size_t)t0, hb0 + i / Dv, i % Dv) : 0.f;
     }
     for (int i = threadIdx.x; i < DPAIRS * D; i += blockDim.x) {
         const int p = i / D, d = i - p * D;
@@ -408,7 +494,7 @@ __global__ void __launch_bounds__(256) seq_attention_decode_kernel(AttnArgs a) {
 #pragma unroll
     for (int p = 0; p < DPAIRS; ++p) slope[p] = (p < nh && a.slopes) ? a.slopes[hb0 + p] : 0.f;
     // ... and the page of the warp's first key tile
-    const int jlo = a.chunk > 0 ? (pos / a.chunk) * a.chunk : 0, jhi = pos;
+    const int jlo = first_key(a, pos), jhi = pos;
     const int ntile = (jhi - jlo) / KT + 1, per = (ntile + a.splits - 1) / a.splits;
     const int tb = (int)blockIdx.z * per, te = min(ntile, tb + per);
     int page_first = 0;
@@ -422,21 +508,24 @@ __global__ void __launch_bounds__(256) seq_attention_decode_kernel(AttnArgs a) {
 #pragma unroll
     for (int p = 0; p < DPAIRS; ++p) {
         m[p] = -INFINITY; l[p] = 0.f;
+        if (a.sinks && p < nh && warp == 0 && blockIdx.z == 0) { m[p] = a.sinks[hb0 + p]; l[p] = 1.f; }   // counted once
 #pragma unroll
         for (int v = 0; v < NV; ++v) acc[p][v] = 0.f;
     }
     const TC* kc = (const TC*)a.kc;
     const TC* vc = (const TC*)a.vc;
     constexpr int KV = 16 / sizeof(TC);
-    const bool kvec = D % KV == 0, vvec = Dv % NV == 0;
+    constexpr int VR = NV >= 16 ? 4 : 8;               // value rows in flight
+    const bool kvec = D % KV == 0 && a.kld % KV == 0;
+    const bool vvec = Dv % NV == 0 && a.vld % NV == 0 && (NV * (int)sizeof(TC) <= 16 || a.vld % KV == 0);
     for (int ti = tb + warp; ti < te; ti += NWARP) {
         const int j = jlo + ti * KT + lane;
         const bool in = j <= jhi;
         long long ko = 0, vo = 0;
         if (in) {
             const int page = ti == tb + warp ? page_first : a.table[(size_t)slot * a.max_pages + j / a.PS], r = j % a.PS;
-            ko = (((long long)page * a.G + g) * a.PS + r) * D;
-            vo = (((long long)page * a.G + g) * a.PS + r) * Dv;
+            ko = (((long long)page * a.G + g) * a.PS + r) * a.kld;
+            vo = (((long long)page * a.G + g) * a.PS + r) * a.vld;
         }
         float s[DPAIRS];
 #pragma unroll
@@ -496,10 +585,10 @@ __global__ void __launch_bounds__(256) seq_attention_decode_kernel(AttnArgs a) {
         }
         const int nvalid = min(KT, jhi - (jlo + ti * KT) + 1);
         const int dv0 = lane * NV;
-        for (int jj0 = 0; jj0 < nvalid; jj0 += 8) {                // eight V rows in flight
-            float vv[8][NV];
+        for (int jj0 = 0; jj0 < nvalid; jj0 += VR) {               // VR value rows in flight
+            float vv[VR][NV];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
+            for (int u = 0; u < VR; ++u) {
                 const long long voj = __shfl_sync(0xffffffffu, vo, (jj0 + u) & 31);
                 if (jj0 + u < nvalid && dv0 < Dv) load_values<TC, NV>(vc + voj + dv0, vvec, Dv - dv0, vv[u]);
                 else {
@@ -508,7 +597,7 @@ __global__ void __launch_bounds__(256) seq_attention_decode_kernel(AttnArgs a) {
                 }
             }
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
+            for (int u = 0; u < VR; ++u) {
 #pragma unroll
                 for (int p = 0; p < DPAIRS; ++p) {
                     const float pj = __shfl_sync(0xffffffffu, pr[p], (jj0 + u) & 31);
@@ -556,7 +645,7 @@ __global__ void __launch_bounds__(256) seq_attention_decode_kernel(AttnArgs a) {
 #pragma unroll
                 for (int uu = 0; uu < GPT; ++uu)
                     if (uu == u) z = gz[uu];
-                if (u >= GPT) z = a.proj[t * a.ld + a.g_off + (size_t)h * Dv + dv];
+                if (u >= GPT) z = gate_logit(a, t, h, dv);
                 o *= 1.f / (1.f + expf(-z));
             }
             a.out[t * a.ldo + (size_t)h * Dv + dv] = o;
@@ -609,7 +698,7 @@ __global__ void __launch_bounds__(256) seq_attention_decode_kernel(AttnArgs a) {
 #pragma unroll
             for (int uu = 0; uu < GPT; ++uu)
                 if (uu == u) z = gz[uu];
-            if (u >= GPT) z = a.proj[t * a.ld + a.g_off + (size_t)h * Dv + dv];
+            if (u >= GPT) z = gate_logit(a, t, h, dv);
             o *= 1.f / (1.f + expf(-z));
         }
         a.out[t * a.ldo + (size_t)h * Dv + dv] = o;
@@ -636,8 +725,9 @@ template <typename TC, int NV>
 int launch_attn_decode(const AttnArgs& a, int tiles, cudaStream_t st) {
     const int rep = a.H / a.G;
     const long long blocks8 = (long long)tiles * a.G * ((rep + DPAIRS_MAX - 1) / DPAIRS_MAX) * a.splits;
-    if (rep > 2 && blocks8 * 4 <= 2 * 148) return launch_attn_decode_dp<TC, NV, 2>(a, tiles, st);
-    return launch_attn_decode_dp<TC, NV, DPAIRS_MAX>(a, tiles, st);
+    if (NV > 8 || (rep > 2 && blocks8 * 4 <= 2 * 148)) return launch_attn_decode_dp<TC, NV, 2>(a, tiles, st);
+    if constexpr (NV <= 8) return launch_attn_decode_dp<TC, NV, DPAIRS_MAX>(a, tiles, st);
+    return 1;
 }
 
 template <typename TC>
@@ -647,7 +737,8 @@ int launch_attn_decode_nv(const AttnArgs& a, int tiles, cudaStream_t st) {
     if (nv <= 2) return launch_attn_decode<TC, 2>(a, tiles, st);
     if (nv <= 4) return launch_attn_decode<TC, 4>(a, tiles, st);
     if (nv <= 8) return launch_attn_decode<TC, 8>(a, tiles, st);
-    set_error("seq_attention failed: value size %d exceeds 256", a.Dv);
+    if (nv <= 16) return launch_attn_decode<TC, 16>(a, tiles, st);
+    set_error("seq_attention failed: value size %d exceeds 512", a.Dv);
     return 1;
 }
 
@@ -676,24 +767,59 @@ int pgk_seq_mixer_prep(float* proj, int ld, int tokens, int heads, int kv_heads,
     return 0;
 }
 
-int pgk_seq_attention(const float* proj, int ld, int q_off, int gate_off, float* out, int ldo, const void* k_cache,
-                      const void* v_cache, int cache_dtype, const int32_t* table, int max_pages, int page_size,
-                      const int32_t* tiles, int n_tiles, const float* slopes, int heads, int kv_heads, int dim, int vdim,
-                      int chunk, float scale, float softcap, int gate, int splits, float* workspace, uint32_t* tickets,
-                      int single_query, void* stream) {
+int pgk_seq_attention_ex(const float* q, int ldq, int q_off, const float* gate_rows, int ldg, int gate_off, int gate_mode,
+                         float* out, int ldo, const void* k_cache, const void* v_cache, int k_ld, int v_ld, int cache_dtype,
+                         const int32_t* table, int max_pages, int page_size, const int32_t* tiles, int n_tiles,
+                         const float* slopes, const float* sinks, int heads, int kv_heads, int dim, int vdim, int chunk,
+                         int window, float scale, float softcap, int splits, float* workspace, uint32_t* tickets,
+                         int single_query, void* stream) {
     PGK_REQUIRE(cache_dtype == 0 || cache_dtype == 2, "seq_attention failed: the cache is float32 (0) or bfloat16 (2), got %d", cache_dtype);
     PGK_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0, "seq_attention failed: invalid head layout");
     PGK_REQUIRE(splits >= 1 && splits <= 64 && (splits == 1 || (workspace && tickets)),
                 "seq_attention failed: 1..64 key slices, more than one needs the workspace and the tickets");
+    PGK_REQUIRE(gate_mode >= 0 && gate_mode <= 2 && (gate_mode == 0 || gate_rows), "seq_attention failed: gate mode %d", gate_mode);
+    PGK_REQUIRE(k_ld >= dim && v_ld >= vdim && chunk >= 0 && window >= 0, "seq_attention failed: row strides %d / %d below the head sizes", k_ld, v_ld);
     if (n_tiles <= 0) return 0;
-    AttnArgs a{proj, ld, q_off, gate_off, out, ldo, k_cache, v_cache, table, max_pages, page_size, (const int4*)tiles, slopes,
-               heads, kv_heads, dim, vdim, chunk, pgk_seq_heads_per_block(heads, kv_heads), gate, scale, softcap, splits, workspace,
-               tickets};
+    AttnArgs a{};
+    a.proj = q; a.ld = ldq; a.q_off = q_off; a.g_off = gate_off;
+    a.out = out; a.ldo = ldo;
+    a.kc = k_cache; a.vc = v_cache; a.table = table; a.max_pages = max_pages; a.PS = page_size;
+    a.gsrc = gate_rows; a.ldg = ldg; a.sinks = sinks; a.window = window; a.kld = k_ld; a.vld = v_ld;
+    a.valias = (k_cache == v_cache && k_ld == v_ld && vdim <= dim) ? 1 : 0;
+    a.tiles = (const int4*)tiles; a.slopes = slopes;
+    a.H = heads; a.G = kv_heads; a.D = dim; a.Dv = vdim; a.chunk = chunk;
+    a.HB = pgk_seq_heads_per_block(heads, kv_heads); a.gate = gate_mode;
+    a.scale = scale; a.cap = softcap; a.splits = splits; a.ws = workspace; a.tickets = tickets;
     if (single_query)       // every tile holds one query: the decoding kernel
         return cache_dtype == 2 ? launch_attn_decode_nv<uint16_t>(a, n_tiles, (cudaStream_t)stream)
                                 : launch_attn_decode_nv<float>(a, n_tiles, (cudaStream_t)stream);
     return cache_dtype == 2 ? launch_attn_nv<uint16_t>(a, n_tiles, (cudaStream_t)stream)
                             : launch_attn_nv<float>(a, n_tiles, (cudaStream_t)stream);
+}
+
+int pgk_seq_attention(const float* proj, int ld, int q_off, int gate_off, float* out, int ldo, const void* k_cache,
+                      const void* v_cache, int cache_dtype, const int32_t* table, int max_pages, int page_size,
+                      const int32_t* tiles, int n_tiles, const float* slopes, int heads, int kv_heads, int dim, int vdim,
+                      int chunk, float scale, float softcap, int gate, int splits, float* workspace, uint32_t* tickets,
+                      int single_query, void* stream) {
+    return pgk_seq_attention_ex(proj, ld, q_off, proj, ld, gate_off, gate ? 1 : 0, out, ldo, k_cache, v_cache, dim, vdim,
+                                cache_dtype, table, max_pages, page_size, tiles, n_tiles, slopes, nullptr, heads, kv_heads,
+                                dim, vdim, chunk, 0, scale, softcap, splits, workspace, tickets, single_query, stream);
+}
+
+// ---- whole-projection norm: q and k are normalised over ALL their heads at once; biases; values = keys before the norm
+int pgk_seq_mixer_prep_all(float* proj, int ld, int tokens, int heads, int kv_heads, int dim, int k_off, const float* q_bias,
+                           const float* k_bias, const float* q_weight, const float* k_weight, float weight_offset, float eps,
+                           void* k_cache, void* v_cache, int cache_dtype, const int32_t* table, int max_pages, int page_size,
+                           const int32_t* slot, const int32_t* pos, void* stream) {
+    PGK_REQUIRE(cache_dtype == 0 || cache_dtype == 2, "seq_mixer_prep_all failed: the cache is float32 (0) or bfloat16 (2), got %d", cache_dtype);
+    PGK_REQUIRE(heads > 0 && kv_heads > 0 && dim > 0, "seq_mixer_prep_all failed: invalid head layout");
+    if (tokens <= 0) return 0;
+    PrepAllArgs a{proj, ld, heads, kv_heads, dim, k_off, q_bias, k_bias, q_weight, k_weight, weight_offset, eps, k_cache, v_cache,
+                  table, max_pages, page_size, slot, pos};
+    if (cache_dtype == 2) PGK_CUDA(launch(mixer_prep_all_kernel<uint16_t>, dim3(tokens), dim3(256), 0, (cudaStream_t)stream, a));
+    else PGK_CUDA(launch(mixer_prep_all_kernel<float>, dim3(tokens), dim3(256), 0, (cudaStream_t)stream, a));
+    return 0;
 }
 int pgk_seq_decode_heads_per_block(void) { return DPAIRS_MAX; }
 

@@ -9,7 +9,11 @@
 //   * groups: `group_off` [E + 1] cuts the rows into E consecutive runs, run e uses weight matrix e (mixture of experts:
 //     the rows are (token, slot) pairs sorted by expert); `a_rows` gathers the rows of A, so the tokens are never copied;
 //   * epilogues: plain; gate/up pairs (W holds gate_j in row 2j and up_j in row 2j + 1, the output is silu(gate) * up,
-//     [M, N / 2]); scale then tanh cap (the logit head).
+//     [M, N / 2]); scale then tanh cap (the logit head); clamped gate/up pairs g = min(gate, limit), u = clamp(up, +-limit),
+//     output g sigmoid(alpha g) (u + 1); C += column vector * product (layer scale and residual add in one pass);
+//     gelu_tanh(product) * gathered table entry (per-layer token inputs);
+//   * batches: grid.z can also walk `batch` independent products whose A columns, matrices and C columns are a fixed number
+//     of elements apart (one product per attention head on slices of the same rows).
 #include "common.cuh"
 #include "../../include/pgk_b200.h"
 
@@ -27,7 +31,20 @@ struct GemmArgs {
     long long w_stride;       // elements between the weight matrices of consecutive groups
     int lda, ldc, M, N, K;
     float scale, cap;
+    const float* colv;        // epilogue 4: [N] factors of the accumulated product
+    const void* aux;          // epilogue 5: table [*, aux_ld] (float32 or bfloat16), entry (aux_rows[m], aux_off + n)
+    const int* aux_rows;
+    int aux_ld, aux_off, aux_dt;
+    long long a_z, c_z;       // batches: elements between the A columns / C columns of consecutive products
 };
+
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+__device__ __forceinline__ float aux_at(const GemmArgs& a, int row, int col) {
+    const size_t i = (size_t)a.aux_rows[row] * a.aux_ld + a.aux_off + col;
+    return a.aux_dt == 2 ? bf16_bits_to_f32(((const uint16_t*)a.aux)[i]) : ((const float*)a.aux)[i];
+}
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
 
@@ -38,11 +55,28 @@ __device__ __forceinline__ void store_pair(const GemmArgs& a, int row, int col, 
         if (col + 1 < a.N) a.C[(size_t)row * a.ldc + (col >> 1)] = silu_f(c0) * c1;
         return;
     }
+    if (EPI == 3) {          // scale = alpha, cap = limit
+        if (col + 1 < a.N) {
+            const float g = fminf(c0, a.cap), u = fminf(fmaxf(c1, -a.cap), a.cap);
+            a.C[(size_t)row * a.ldc + (col >> 1)] = g / (1.f + expf(-a.scale * g)) * (u + 1.f);
+        }
+        return;
+    }
     if (EPI == 2) {
         c0 *= a.scale; c1 *= a.scale;
         if (a.cap > 0.f) { c0 = a.cap * tanhf(c0 / a.cap); c1 = a.cap * tanhf(c1 / a.cap); }
     }
     float* p = a.C + (size_t)row * a.ldc + col;
+    if (EPI == 4) {
+        if (col < a.N) p[0] = fmaf(a.colv[col], c0, p[0]);
+        if (col + 1 < a.N) p[1] = fmaf(a.colv[col + 1], c1, p[1]);
+        return;
+    }
+    if (EPI == 5) {
+        if (col < a.N) p[0] = gelu_tanh_f(c0) * aux_at(a, row, col);
+        if (col + 1 < a.N) p[1] = gelu_tanh_f(c1) * aux_at(a, row, col + 1);
+        return;
+    }
     if (col < a.N) p[0] = c0;
     if (col + 1 < a.N) p[1] = c1;
 }
@@ -64,6 +98,8 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
 template <int EPI>
 __global__ void __launch_bounds__(128) gemm_rows_bf16_kernel(GemmArgs a) {
     const int e = blockIdx.z;
+    a.A += (size_t)e * a.a_z;
+    a.C += (size_t)e * a.c_z;
     const int m_begin = a.group_off ? a.group_off[e] : 0;
     const int m_end = a.group_off ? a.group_off[e + 1] : a.M;
     const int m0 = m_begin + blockIdx.y * BM;
@@ -178,6 +214,8 @@ __global__ void __launch_bounds__(128) gemm_rows_bf16_kernel(GemmArgs a) {
 template <int EPI>
 __global__ void __launch_bounds__(128) gemm_rows_f32_kernel(GemmArgs a) {
     const int e = blockIdx.z;
+    a.A += (size_t)e * a.a_z;
+    a.C += (size_t)e * a.c_z;
     const int m_begin = a.group_off ? a.group_off[e] : 0;
     const int m_end = a.group_off ? a.group_off[e + 1] : a.M;
     const int m0 = m_begin + blockIdx.y * BM;
@@ -261,7 +299,9 @@ __global__ void __launch_bounds__(FEW_MAX_WARPS * 32) gemm_few_rows_kernel(GemmA
     extern __shared__ __align__(16) float xs[];                 // [rows][K]
     const int r0 = blockIdx.y * rows_per_block;
     const int nr = min(rows_per_block, a.M - r0);
-    const int grp = a.row_group ? a.row_group[r0] : 0;
+    const int grp = a.row_group ? a.row_group[r0] : (int)blockIdx.z;
+    a.A += (size_t)blockIdx.z * a.a_z;
+    a.C += (size_t)blockIdx.z * a.c_z;
     const TW* W = (const TW*)a.W + (size_t)grp * a.w_stride;
     constexpr int VEC = WLoad<TW>::VEC;
     const bool vec = (a.K % VEC == 0) && (((uintptr_t)W & 15) == 0);
@@ -367,7 +407,7 @@ int launch_many(const GemmArgs& a, int wdt, int groups, int max_rows, cudaStream
 }
 
 template <typename TW, int EPI, bool ROUND>
-int launch_few_t(const GemmArgs& a, int rows_per_block, cudaStream_t st) {
+int launch_few_t(const GemmArgs& a, int rows_per_block, cudaStream_t st, int batch) {
     const size_t smem = (size_t)rows_per_block * a.K * sizeof(float);
     static size_t configured = 0;
     if (smem > 48 * 1024 && smem > configured) {
@@ -376,15 +416,15 @@ int launch_few_t(const GemmArgs& a, int rows_per_block, cudaStream_t st) {
     }
     // a block's shared memory decides how many blocks fit an SM: keep about 16 warps per SM streaming
     const int warps = smem <= 48 * 1024 ? 4 : (smem <= 100 * 1024 ? 8 : FEW_MAX_WARPS);
-    dim3 grid(((a.N + 1) / 2 + warps - 1) / warps, (a.M + rows_per_block - 1) / rows_per_block);
+    dim3 grid(((a.N + 1) / 2 + warps - 1) / warps, (a.M + rows_per_block - 1) / rows_per_block, batch);
     PGK_CUDA(launch(gemm_few_rows_kernel<TW, EPI, ROUND>, grid, dim3(warps * 32), smem, st, a, rows_per_block));
     return 0;
 }
 
 template <int EPI>
-int launch_few(const GemmArgs& a, int wdt, int rows_per_block, cudaStream_t st) {
-    if (wdt == 2) return launch_few_t<uint16_t, EPI, true>(a, rows_per_block, st);
-    return launch_few_t<float, EPI, false>(a, rows_per_block, st);
+int launch_few(const GemmArgs& a, int wdt, int rows_per_block, cudaStream_t st, int batch = 1) {
+    if (wdt == 2) return launch_few_t<uint16_t, EPI, true>(a, rows_per_block, st, batch);
+    return launch_few_t<float, EPI, false>(a, rows_per_block, st, batch);
 }
 
 }  // namespace
@@ -401,7 +441,7 @@ int pgk_gemm_rows_f32(const float* A, int lda, const int32_t* a_rows, const void
     const int G = group_off ? groups : 1;
     const int rows = group_off ? max_rows : M;
     if (rows <= 0 || G <= 0) return 0;
-    GemmArgs a{A, a_rows, W, C, group_off, nullptr, w_group_stride, lda, ldc, M, N, K, scale, cap};
+    GemmArgs a{A, a_rows, W, C, group_off, nullptr, w_group_stride, lda, ldc, M, N, K, scale, cap, nullptr, nullptr, nullptr, 0, 0, 0, 0, 0};
     cudaStream_t st = (cudaStream_t)stream;
     if (epilogue == 0) return launch_many<0>(a, wdt, G, rows, st);
     if (epilogue == 1) return launch_many<1>(a, wdt, G, rows, st);
@@ -420,11 +460,50 @@ int pgk_gemm_few_rows_f32(const float* A, int lda, const int32_t* a_rows, const 
     PGK_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_few_rows_f32 failed: unknown epilogue %d", epilogue);
     PGK_REQUIRE(epilogue != 1 || N % 2 == 0, "gemm_few_rows_f32 failed: the gate/up epilogue needs an even N");
     if (M == 0) return 0;
-    GemmArgs a{A, a_rows, W, C, nullptr, row_group, w_group_stride, lda, ldc, M, N, K, scale, cap};
+    GemmArgs a{A, a_rows, W, C, nullptr, row_group, w_group_stride, lda, ldc, M, N, K, scale, cap, nullptr, nullptr, nullptr, 0, 0, 0, 0, 0};
     cudaStream_t st = (cudaStream_t)stream;
     if (epilogue == 0) return launch_few<0>(a, wdt, rows_per_block, st);
     if (epilogue == 1) return launch_few<1>(a, wdt, rows_per_block, st);
     return launch_few<2>(a, wdt, rows_per_block, st);
+}
+
+
+/* The general form: `batch` independent products (A columns a_batch apart, matrices w_batch apart, C columns c_batch apart)
+ * over the same M rows, every epilogue.  rows_per_block > 0 selects the few-row kernel (M <= 8 rows share one pass over the
+ * weights), 0 the tiled kernel. */
+int pgk_gemm_seq_f32(const float* A, int lda, long long a_batch, const void* W, int wdt, long long w_batch, float* C, int ldc,
+                     long long c_batch, int M, int N, int K, int batch, int epilogue, float p0, float p1, const float* col_scale,
+                     const void* aux, int aux_dtype, const int32_t* aux_rows, int aux_ld, int aux_off, int rows_per_block,
+                     void* stream) {
+    PGK_REQUIRE(wdt == 0 || wdt == 2, "gemm_seq_f32 failed: weights must be float32 (0) or bfloat16 (2), got %d", wdt);
+    PGK_REQUIRE(N > 0 && K > 0 && M >= 0 && batch >= 1, "gemm_seq_f32 failed: invalid shape M=%d N=%d K=%d batch=%d", M, N, K, batch);
+    PGK_REQUIRE(epilogue >= 0 && epilogue <= 5, "gemm_seq_f32 failed: unknown epilogue %d", epilogue);
+    PGK_REQUIRE((epilogue != 1 && epilogue != 3) || N % 2 == 0, "gemm_seq_f32 failed: a gate/up epilogue needs an even N");
+    PGK_REQUIRE(epilogue != 4 || col_scale, "gemm_seq_f32 failed: the scaled-accumulate epilogue needs its column factors");
+    PGK_REQUIRE(epilogue != 5 || (aux && aux_rows && (aux_dtype == 0 || aux_dtype == 2)), "gemm_seq_f32 failed: the gather epilogue needs its table and rows");
+    PGK_REQUIRE(rows_per_block >= 0 && rows_per_block <= RMAX, "gemm_seq_f32 failed: 0..%d rows per block", RMAX);
+    PGK_REQUIRE(rows_per_block == 0 || (size_t)rows_per_block * K * 4 <= 200 * 1024, "gemm_seq_f32 failed: %d rows of K=%d do not fit shared memory", rows_per_block, K);
+    if (M == 0) return 0;
+    GemmArgs a{A, nullptr, W, C, nullptr, nullptr, w_batch, lda, ldc, M, N, K, p0, p1, col_scale, aux, aux_rows, aux_ld, aux_off, aux_dtype, a_batch, c_batch};
+    cudaStream_t st = (cudaStream_t)stream;
+    if (rows_per_block > 0) {
+        switch (epilogue) {
+            case 0: return launch_few<0>(a, wdt, rows_per_block, st, batch);
+            case 1: return launch_few<1>(a, wdt, rows_per_block, st, batch);
+            case 2: return launch_few<2>(a, wdt, rows_per_block, st, batch);
+            case 3: return launch_few<3>(a, wdt, rows_per_block, st, batch);
+            case 4: return launch_few<4>(a, wdt, rows_per_block, st, batch);
+            default: return launch_few<5>(a, wdt, rows_per_block, st, batch);
+        }
+    }
+    switch (epilogue) {
+        case 0: return launch_many<0>(a, wdt, batch, M, st);
+        case 1: return launch_many<1>(a, wdt, batch, M, st);
+        case 2: return launch_many<2>(a, wdt, batch, M, st);
+        case 3: return launch_many<3>(a, wdt, batch, M, st);
+        case 4: return launch_many<4>(a, wdt, batch, M, st);
+        default: return launch_many<5>(a, wdt, batch, M, st);
+    }
 }
 
 }  // extern "C"

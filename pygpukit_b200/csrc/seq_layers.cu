@@ -1,7 +1,8 @@
 // seq_layers.cu -- the row-wise pieces of the token-major models, all in float32: embedding rows, the fused
 // "sum the sublayer's parts -> LayerNorm -> add to the residual" step, row gather + LayerNorm (final norm of the wanted
 // rows), and the mixture-of-experts router (softmax over all experts, group-limited top-k, renormalised weights) with the
-// per-expert row lists the grouped GEMM consumes.
+// per-expert row lists the grouped GEMM consumes; and the RMS norm of rows (weight with an offset, optional second summand
+// that is written back, optional accumulation into the output) that the pre-norm blocks are built from.
 #include "common.cuh"
 #include "../../include/pgk_b200.h"
 
@@ -84,6 +85,37 @@ __global__ void __launch_bounds__(256) combine_norm_kernel(NormArgs a) {
         const float v = (y[i] - mean) * inv * a.gamma[i] + a.beta[i];
         float* o = a.out + (size_t)t * a.W + i;
         *o = a.add ? *o + v : v;
+    }
+}
+
+// ---------------------------------------------------------------- RMS norm of rows
+// v = x[src] (+ add[t]);  sum_out[t] = v (when given);  r = v / sqrt(mean(v^2) + eps) * (w_off + w);
+// accumulate: out[t] += r, else out[t] = r.  `out` may be `x` (the row is staged in shared memory first).
+struct RmsArgs {
+    const float* x; const int* src_rows; const float* add; float* sum_out;
+    const float* w; float w_off, eps;
+    float* out; int W; int accumulate;
+};
+
+__global__ void __launch_bounds__(256) rms_norm_rows_kernel(RmsArgs a) {
+    extern __shared__ float y[];
+    __shared__ float red[8];
+    const int t = blockIdx.x;
+    const size_t srow = a.src_rows ? (size_t)a.src_rows[t] : (size_t)t;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < a.W; i += blockDim.x) {
+        float v = a.x[srow * a.W + i];
+        if (a.add) v += a.add[(size_t)t * a.W + i];
+        y[i] = v;
+        q = fmaf(v, v, q);
+    }
+    const float inv = 1.f / sqrtf(block_sum256(q, red) / (float)a.W + a.eps);
+    for (int i = threadIdx.x; i < a.W; i += blockDim.x) {
+        const float v = y[i];
+        if (a.sum_out) a.sum_out[(size_t)t * a.W + i] = v;
+        const float r = v * inv * (a.w_off + a.w[i]);
+        float* o = a.out + (size_t)t * a.W + i;
+        *o = a.accumulate ? *o + r : r;
     }
 }
 
@@ -212,6 +244,22 @@ int pgk_combine_layernorm_f32(const float* base, const int32_t* src_rows, const 
         configured = true;
     }
     PGK_CUDA(launch(combine_norm_kernel, dim3(rows), dim3(256), smem, (cudaStream_t)stream, a));
+    return 0;
+}
+
+int pgk_rms_norm_rows_f32(const float* x, const int32_t* src_rows, const float* add, float* sum_out, const float* weight,
+                          float weight_offset, float eps, float* out, int rows, int width, int accumulate, void* stream) {
+    PGK_REQUIRE(width > 0 && width * 4 <= 160 * 1024, "rms_norm_rows_f32 failed: width %d out of range", width);
+    PGK_REQUIRE(!(sum_out && src_rows), "rms_norm_rows_f32 failed: the sum is written back only without a row gather");
+    if (rows <= 0) return 0;
+    RmsArgs a{x, src_rows, add, sum_out, weight, weight_offset, eps, out, width, accumulate};
+    const size_t smem = (size_t)width * 4;
+    static bool configured = false;
+    if (smem > 48 * 1024 && !configured) {
+        PGK_CUDA(cudaFuncSetAttribute(rms_norm_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        configured = true;
+    }
+    PGK_CUDA(launch(rms_norm_rows_kernel, dim3(rows), dim3(256), smem, (cudaStream_t)stream, a));
     return 0;
 }
 

@@ -89,19 +89,36 @@ class RowBuffers:
         from ..core.dtypes import float32
         W = config.hidden_size
         proj = attn = gv = top = ff = sff = experts = 1
+        q_up = q_abs = lat = hout = 1
         for L in config.layers:
             m = L.mixer
-            proj = max(proj, m.heads * m.dim + m.kv_heads * m.dim + m.kv_heads * m.vdim + (m.heads * m.vdim if m.out_gate else 0))
-            attn = max(attn, m.heads * m.vdim)
-            gv = max(gv, m.kv_heads * m.vdim)
-            if L.mlp is not None:
+            proj = max(proj, m.proj_cols)
+            if m.kind == "latent_attention":
+                q_up = max(q_up, m.heads * (m.dim + m.rot_dim))
+                q_abs = max(q_abs, m.heads * (m.kv_rank + m.rot_dim))
+                lat = max(lat, m.heads * m.kv_rank)
+                hout = max(hout, m.heads * m.vdim)
+            else:
+                attn = max(attn, m.attn_cols)
+                gv = max(gv, m.kv_heads * m.vdim)
+            if L.mlp is not None and L.mlp.kind == "dense":
+                sff = max(sff, L.mlp.ff)
+            elif L.mlp is not None:
                 top, ff, sff = max(top, L.mlp.top), max(ff, L.mlp.ff), max(sff, L.mlp.shared_ff)
                 experts = max(experts, L.mlp.experts)
         R = self.rows = max(8, int(rows))
         self.x = GPUArray((R, W), float32)
         self.y = GPUArray((R, W), float32)
+        parallel = getattr(config, "block", "post_norm") == "parallel"
+        self.h = GPUArray((R, W), float32) if parallel else None                        # the block's normed rows
+        self.x0 = GPUArray((R, W), float32) if getattr(config, "loop_times", 1) > 1 else None   # embedding output
+        self.side = GPUArray((R, max(1, getattr(config, "side_dim", 0))), float32)
         self.proj = GPUArray((R, proj), float32)
         self.attn = GPUArray((R, attn), float32)
+        self.q_up = GPUArray((R, q_up), float32)            # latent attention: queries, absorbed queries + rotated
+        self.q_abs = GPUArray((R, q_abs), float32)          # tails, latent-space outputs, per-head values
+        self.latent_out = GPUArray((R, lat), float32)
+        self.head_out = GPUArray((R, hout), float32)
         self.v_first = GPUArray((R, gv), float32)
         self.moe_idx = GPUArray((R * top,), int32)
         self.moe_rank = GPUArray((R * top,), int32)
@@ -114,7 +131,7 @@ class RowBuffers:
         self.moe_off = GPUArray((experts + 1,), int32)
         self.moe_act = GPUArray((R * top, ff), float32)
         self.moe_parts = GPUArray((R * top, W), float32)
-        self.shared_act = GPUArray((R, sff), float32)
+        self.shared_act = GPUArray((R, sff), float32)       # shared expert / dense feed-forward activations
 
 
 __all__.append("RowBuffers")

@@ -234,7 +234,14 @@ class AttentionMixerSpec:
     """One attention mixer: H query heads of size `dim`, G key/value heads, values of size `vdim`; score =
     scale q.k, squashed to softcap tanh(. / softcap) when softcap > 0, minus a per-head distance slope when
     `distance_bias`; `chunk` > 0 limits a query to the keys of its own chunk of positions; RMS norm on q and k
-    (`qk_norm`), value mixing with the first mixing layer (`v_mix`), sigmoid output gate (`out_gate`)."""
+    (`qk_norm`), value mixing with the first mixing layer (`v_mix`), sigmoid output gate (`out_gate`).
+
+    `window` > 0: a query sees itself and the window - 1 positions before it.  `sink`: "none", "zero" (the softmax
+    denominator gains exp(0) = 1) or "learned" (it gains exp(s_h), one number per head).  `norm_scope` "head": q and k are
+    normalised head by head with one weight vector of size dim; "all": over the whole projection with weights of the
+    projection's size.  `qk_bias`: the q and k projections have biases.  `values` "own": a value projection; "keys": the
+    values are the keys as projected, before their norm (no value matrix; vdim == dim).  `gate_per_head`: the output
+    gate is one number per head instead of one per output element."""
     heads: int
     kv_heads: int
     dim: int
@@ -246,10 +253,98 @@ class AttentionMixerSpec:
     qk_norm: bool = True
     out_gate: bool = True
     distance_bias: bool = True
+    window: int = 0
+    sink: str = "none"
+    norm_scope: str = "head"
+    qk_bias: bool = False
+    values: str = "own"
+    gate_per_head: bool = False
+
+    kind = "attention"
+
+    @property
+    def gate_cols(self) -> int:
+        return 0 if not self.out_gate else (self.heads if self.gate_per_head else self.heads * self.vdim)
+
+    @property
+    def proj_cols(self) -> int:
+        """columns of the fused projection [q | k | v | gate]"""
+        v = self.kv_heads * self.vdim if self.values == "own" else 0
+        return self.heads * self.dim + self.kv_heads * self.dim + v + self.gate_cols
+
+    @property
+    def attn_cols(self) -> int:
+        return self.heads * self.vdim
+
+    def cache_shape(self) -> tuple[int, int, int]:
+        """(key/value heads, key row size, value row size) of this mixer's cache pages"""
+        return (self.kv_heads, self.dim, self.vdim)
 
     def slopes(self) -> list[float]:
         """slope of head h = 2^(-8 (h + 1) / H)"""
         return [2.0 ** (-8.0 * (h + 1) / self.heads) for h in range(self.heads)] if self.distance_bias else []
+
+
+@dataclass(frozen=True)
+class LatentMixerSpec:
+    """Latent attention: queries through a latent of size `q_rank` (0: projected directly), keys and values through one
+    latent of size `kv_rank` per position plus `rot_dim` rotated key dimensions shared by the heads.  Per head `dim`
+    unrotated + `rot_dim` rotated query/key dimensions and `vdim` value dimensions; the rotation turns the first
+    `rot_dims` of the rotated part (interleaved pairs, base `rot_base`); causal; `sink` and the per-head gate as in
+    AttentionMixerSpec.  Only the latent and the rotated key part are cached."""
+    heads: int
+    dim: int
+    rot_dim: int
+    vdim: int
+    kv_rank: int
+    q_rank: int
+    scale: float
+    rot_dims: int
+    rot_base: float
+    sink: str = "learned"
+    out_gate: bool = True
+    gate_per_head: bool = True
+
+    kind = "latent_attention"
+    kv_heads = 1
+    chunk = 0
+    window = 0
+
+    @property
+    def gate_cols(self) -> int:
+        return 0 if not self.out_gate else (self.heads if self.gate_per_head else self.heads * self.vdim)
+
+    @property
+    def proj_cols(self) -> int:
+        """columns of the fused projection [query latent | key/value latent + rotated key | gate]"""
+        return self.q_rank + self.kv_rank + self.rot_dim + self.gate_cols
+
+    @property
+    def attn_cols(self) -> int:
+        """per token: the absorbed queries (and, later, the latent-space outputs) of all heads"""
+        return self.heads * (self.kv_rank + self.rot_dim)
+
+    def cache_shape(self) -> tuple[int, int, int]:
+        return (1, self.kv_rank + self.rot_dim, 0)          # value rows are a prefix of the key rows
+
+    def inv_freq(self) -> list[float]:
+        """angle per position of pair i = rot_base^(-2 i / rot_dims)"""
+        return [self.rot_base ** (-2.0 * i / self.rot_dims) for i in range(self.rot_dims // 2)]
+
+
+@dataclass(frozen=True)
+class DenseSpec:
+    """Gated dense feed-forward: g = W_gate h, u = W_up h, output W_down act(g, u).  activation "silu": silu(g) u;
+    "clamped_swish": g <- min(g, limit), u <- clamp(u, -limit, limit), g sigmoid(alpha g) (u + 1)."""
+    ff: int
+    activation: str = "silu"
+    limit: float = 0.0
+    alpha: float = 1.702
+
+    kind = "dense"
+    top = 1
+    experts = 1
+    shared_ff = 0
 
 
 @dataclass(frozen=True)
@@ -263,11 +358,13 @@ class MoESpec:
     group_keep: int = 1
     shared_ff: int = 0
 
+    kind = "moe"
+
 
 @dataclass(frozen=True)
 class LayerSpec:
-    mixer: AttentionMixerSpec
-    mlp: MoESpec | None
+    mixer: "AttentionMixerSpec | LatentMixerSpec"
+    mlp: "MoESpec | DenseSpec | None"
 
 
 @dataclass
@@ -281,10 +378,32 @@ class LayeredConfig:
     norm_eps: float = 1e-5
     logit_scale: float = 1.0
     logit_softcap: float = 0.0
+    # block form: "post_norm" x += LN(sublayer(x)) twice; "parallel" h = norm(x), x += s1 mixer(h) + s2 ff(h)
+    block: str = "post_norm"
+    norm: str = "layernorm"            # "layernorm" (weight + bias) or "rmsnorm_1p" (x / rms * (1 + w))
+    embed_norm: bool = False           # the model's norm on the embedding output
+    layer_scale: bool = False          # per-channel factors on the mixer's and the feed-forward's result
+    side_dim: int = 0                  # > 0: a per-layer token input of this size after every layer
+    # layers loop_start .. loop_stop - 1 run loop_times times in a row with the same weights (each pass with its own cache);
+    # before every pass but the first the embedding output is added to the residual stream
+    loop_start: int = 0
+    loop_stop: int = 0
+    loop_times: int = 1
 
     @property
     def num_layers(self) -> int:
         return len(self.layers)
+
+    def layer_runs(self) -> list[tuple[int, bool]]:
+        """The order in which layers run: (layer index, whether the embedding output is added first).  The position in
+        this list names the run's cache."""
+        n = len(self.layers)
+        if self.loop_times <= 1 or self.loop_stop <= self.loop_start:
+            return [(i, False) for i in range(n)]
+        runs = [(i, False) for i in range(self.loop_start)]
+        for t in range(self.loop_times):
+            runs += [(i, t > 0 and i == self.loop_start) for i in range(self.loop_start, self.loop_stop)]
+        return runs + [(i, False) for i in range(self.loop_stop, n)]
 
 
 def _dolurax_config(d: dict) -> LayeredConfig:
@@ -320,8 +439,56 @@ def _dolurax_config(d: dict) -> LayeredConfig:
                          logit_softcap=float(d.get("logit_softcap") or 0.0))
 
 
+def _turutar_config(d: dict) -> LayeredConfig:
+    """Turutar: parallel pre-norm blocks (one RMS norm with a weight stored around zero, mixer and feed-forward both read
+    it, layer scales on both results) of windowed attention whose values are its keys, or latent attention with rotary
+    positions; clamped gated feed-forward; a per-layer token input after every layer; an optional loop over a run of
+    layers.  Constants the design fixes live here: the zero sink of the windowed mixer, the learned one of the latent
+    mixer, per-head gates, alpha = 1.702."""
+    W = int(d["width"])
+    layers = []
+    for i, L in enumerate(d["layers"]):
+        m, kind = L["mixer"], L.get("type")
+        if kind == "attention":
+            heads, dim = int(m["heads"]), int(m["dim"])
+            kv = int(m.get("kv_heads") or heads)
+            vdim = int(m.get("vdim") or dim)
+            if heads % kv:
+                raise ValueError(f"Turutar: layer {i}: {heads} heads over {kv} key/value heads")
+            if vdim != dim:
+                raise ValueError(f"Turutar: layer {i}: the values are the keys, value size {vdim} must equal {dim}")
+            mixer = AttentionMixerSpec(heads=heads, kv_heads=kv, dim=dim, vdim=vdim, scale=float(m["scale"]),
+                                       window=int((m.get("mask") or {}).get("size") or 0), sink="zero", norm_scope="all",
+                                       qk_bias=True, values="keys", gate_per_head=True, distance_bias=False)
+        elif kind == "latent_attention":
+            rot = m.get("rot") or {}
+            rot_dim = int(m["rot_dim"])
+            mixer = LatentMixerSpec(heads=int(m["heads"]), dim=int(m["dim"]), rot_dim=rot_dim, vdim=int(m["vdim"]),
+                                    kv_rank=int(m["kv_rank"]), q_rank=int(m["q_rank"]), scale=float(m["scale"]),
+                                    rot_dims=int(rot.get("dims", rot_dim)), rot_base=float(rot.get("base", 10000.0)))
+            if mixer.rot_dims % 2 or mixer.rot_dims > rot_dim:
+                raise ValueError(f"Turutar: layer {i}: {mixer.rot_dims} rotated dimensions in a part of {rot_dim}")
+        else:
+            raise ValueError(f"Turutar: layer {i} has unknown type {kind!r}")
+        mlp = None
+        f = L.get("mlp")
+        if f:
+            if f.get("kind") != "dense":
+                raise ValueError(f"Turutar: layer {i} has unknown feed-forward kind {f.get('kind')!r}")
+            mlp = DenseSpec(ff=int(f["ff"]), activation="clamped_swish", limit=float(f["limit"]))
+        layers.append(LayerSpec(mixer, mlp))
+    lp = d.get("loop") or {}
+    start, stop, times = int(lp.get("start", 0)), int(lp.get("stop", 0)), int(lp.get("times", 1))
+    if not 0 <= start <= stop <= len(layers) or times < 1:
+        raise ValueError(f"Turutar: loop {start}..{stop} x {times} does not fit {len(layers)} layers")
+    return LayeredConfig(architecture="Turutar", vocab_size=int(d["vocab"]), hidden_size=W, layers=layers,
+                         norm_eps=float((d.get("norm") or {}).get("eps", 1e-6)), block="parallel", norm="rmsnorm_1p",
+                         embed_norm=True, layer_scale=True, side_dim=int((d.get("token_side") or {}).get("dim") or 0),
+                         loop_start=start, loop_stop=stop, loop_times=times)
+
+
 # config.json "architecture" -> parser (the model registry of the layered families)
-LAYERED_ARCHITECTURES = {"dolurax": _dolurax_config}
+LAYERED_ARCHITECTURES = {"dolurax": _dolurax_config, "turutar": _turutar_config}
 
 
 def layered_config_from_json(d: dict) -> LayeredConfig | None:
@@ -332,5 +499,5 @@ def layered_config_from_json(d: dict) -> LayeredConfig | None:
 
 __all__ = ["ModelSpec", "TransformerConfig", "GPT2Config", "LlamaConfig", "Qwen3Config", "GPT2_SPEC", "LLAMA_SPEC",
            "QWEN2_SPEC", "QWEN3_SPEC", "QWEN3_MOE_SPEC", "MIXTRAL_SPEC", "MODEL_SPECS", "detect_model_spec",
-           "named_config", "AttentionMixerSpec", "MoESpec", "LayerSpec", "LayeredConfig",
+           "named_config", "AttentionMixerSpec", "LatentMixerSpec", "DenseSpec", "MoESpec", "LayerSpec", "LayeredConfig",
            "LAYERED_ARCHITECTURES", "layered_config_from_json"]

@@ -87,12 +87,14 @@ class PostNormBlock:
         self.mixer, self.mlp = mixer, mlp
         self.norm1, self.norm2, self.eps = norm1, norm2, float(eps)
 
-    def forward(self, ctx, x: GPUArray) -> None:
+    def forward(self, ctx, x: GPUArray, cache_index: int | None = None, add_ptr: int | None = None) -> None:
         from ..._lib import api
         from ...core.stream import current_stream_handle as _st
+        if add_ptr is not None:
+            raise ValueError("PostNormBlock: no loop passes in this block form")
         T, W = ctx.T, x.shape[1]
         y = ctx.buf.y
-        self.mixer.forward(ctx, x, y)
+        self.mixer.forward(ctx, x, y, cache_index)
         api.combine_layernorm_f32(y.device_ptr, None, None, None, None, 0, self.norm1[0].device_ptr,
                                   self.norm1[1].device_ptr, self.eps, x.device_ptr, T, W, 1, _st())
         if self.mlp is not None:
@@ -108,4 +110,38 @@ class PostNormBlock:
         return n
 
 
-__all__ = ["TransformerBlock", "PostNormBlock"]
+class ParallelBlock:
+    """Block of the token-major models with ONE norm in front of both sublayers: h = norm(x), then
+    x += s1 * mixer(h) + s2 * ff(h) with per-channel factors s1, s2 (layer scales; ones without them), then the optional
+    per-layer token input.  The two scaled adds ride in the epilogues of the output projection and of the down projection
+    (C += s * product), so the block adds no launch of its own beyond the norm.  `add_ptr`: rows added to x before the norm
+    and written back (the embedding output at the start of a loop pass) -- same launch."""
+
+    def __init__(self, norm, mixer, mixer_scale: GPUArray, mlp, mlp_scale: "GPUArray | None", side=None):
+        self.norm, self.mixer, self.mlp, self.side = norm, mixer, mlp, side
+        self.mixer_scale, self.mlp_scale = mixer_scale, mlp_scale
+        if mlp is not None and mlp_scale is None:
+            raise ValueError("ParallelBlock: the feed-forward needs its scale vector")
+
+    def forward(self, ctx, x: GPUArray, cache_index: int | None = None, add_ptr: int | None = None) -> None:
+        T, W = ctx.T, x.shape[1]
+        h = ctx.buf.h
+        self.norm.forward(x.device_ptr, h.device_ptr, T, W, add_ptr=add_ptr,
+                          sum_out_ptr=x.device_ptr if add_ptr is not None else None)
+        self.mixer.forward(ctx, h, x, cache_index, out_scale=self.mixer_scale.device_ptr)
+        if self.mlp is not None:
+            self.mlp.forward(ctx, h.device_ptr, x.device_ptr, out_scale=self.mlp_scale.device_ptr)
+        if self.side is not None:
+            self.side.forward(ctx, x)
+
+    @property
+    def weight_bytes(self) -> int:
+        n = self.mixer.weight_bytes + self.norm.nbytes + self.mixer_scale.nbytes
+        if self.mlp is not None:
+            n += self.mlp.weight_bytes + self.mlp_scale.nbytes
+        if self.side is not None:
+            n += self.side.weight_bytes
+        return n
+
+
+__all__ = ["TransformerBlock", "PostNormBlock", "ParallelBlock"]

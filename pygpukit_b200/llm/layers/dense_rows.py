@@ -1,0 +1,42 @@
+"""Gated dense feed-forward of the token-major models (net-new; beside `MLP`, which serves bfloat16 rows one sequence at
+a time, and `GroupedRouterMoE`).  Two launches: the fused gate/up product whose epilogue applies the activation to
+interleaved (gate_j, up_j) pairs, and the down projection.
+
+  activation "silu":           silu(g) * u
+  activation "clamped_swish":  g <- min(g, limit), u <- clamp(u, -limit, limit), g * sigmoid(alpha g) * (u + 1)
+
+`forward(..., out_scale=ptr)` adds `out_scale * result` to `out` in the down projection's epilogue (layer scale and
+residual add of a parallel block); without it the result is stored.
+"""
+from __future__ import annotations
+
+from ..config import DenseSpec
+from .linear import LinearRows
+
+
+class GatedDenseRows:
+    def __init__(self, spec: DenseSpec, gate_up: LinearRows, down: LinearRows):
+        if spec.activation not in ("silu", "clamped_swish"):
+            raise ValueError(f"GatedDenseRows: unknown activation {spec.activation!r}")
+        if gate_up.out_features != 2 * spec.ff or down.in_features != spec.ff:
+            raise ValueError("GatedDenseRows: matrices do not match the feed-forward size")
+        self.spec, self.gate_up, self.down = spec, gate_up, down
+
+    @property
+    def weight_bytes(self) -> int:
+        return self.gate_up.nbytes + self.down.nbytes
+
+    def forward(self, ctx, h_ptr: int, out_ptr: int, out_scale: int | None = None) -> None:
+        sp, T = self.spec, ctx.T
+        W, act = self.gate_up.in_features, ctx.buf.shared_act
+        if sp.activation == "silu":
+            self.gate_up.forward_seq(h_ptr, W, T, act.device_ptr, sp.ff, epilogue=1)
+        else:
+            self.gate_up.forward_seq(h_ptr, W, T, act.device_ptr, sp.ff, epilogue=3, p0=sp.alpha, p1=sp.limit)
+        if out_scale is None:
+            self.down.forward_seq(act.device_ptr, sp.ff, T, out_ptr, self.down.out_features, epilogue=0)
+        else:
+            self.down.forward_seq(act.device_ptr, sp.ff, T, out_ptr, self.down.out_features, epilogue=4, col_scale=out_scale)
+
+
+__all__ = ["GatedDenseRows"]

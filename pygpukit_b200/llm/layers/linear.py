@@ -246,7 +246,9 @@ class LinearRows:
     """Linear layer of the token-major models (net-new): float32 activations [rows, K], weights [N, K] (or a stack
     [E, N, K] of expert matrices) in bfloat16 or float32, float32 accumulation and output.  Many rows run as tiled
     GEMMs (tensor cores for bfloat16 weights), up to eight rows through the streaming few-row kernel.  epilogue:
-    0 plain, 1 gate/up pairs -> silu(gate) * up (rows of W interleaved by `interleave_gate_up`), 2 scale + tanh cap."""
+    0 plain, 1 gate/up pairs -> silu(gate) * up (rows of W interleaved by `interleave_gate_up`), 2 scale + tanh cap;
+    `forward_seq` adds 3 clamped gate/up pairs, 4 scaled accumulation into the output, 5 gelu * gathered table entry,
+    and batches of per-head products."""
 
     FEW = 8
     FEW_SMEM_FLOATS = 40960          # 160 KB of activations per block
@@ -281,6 +283,21 @@ class LinearRows:
         else:
             api.gemm_rows_f32(x_ptr, ldx, a_rows, self.weight.device_ptr, self.wdt, 0, out_ptr, ldo, rows, N, K, None, 1,
                               rows, self.epilogue, self.scale, self.cap, _st())
+
+    def forward_seq(self, x_ptr: int, ldx: int, rows: int, out_ptr: int, ldo: int, *, epilogue: int | None = None,
+                    p0: float | None = None, p1: float | None = None, col_scale: int | None = None, aux: tuple | None = None,
+                    batch: int = 1, a_batch: int = 0, c_batch: int = 0) -> None:
+        """The general product (pgk_gemm_seq_f32).  epilogue 3: clamped gate/up pairs (p0 = alpha, p1 = limit); 4: out +=
+        col_scale * product (col_scale: device pointer of [N] floats); 5: gelu_tanh(product) * aux entry, aux = (table
+        pointer, dtype code, row-index pointer, row stride, column offset).  batch > 1: the weight is a stack [batch, N, K]
+        and product b reads x columns from b * a_batch and writes out columns from b * c_batch."""
+        N, K = self.out_features, self.in_features
+        epi = self.epilogue if epilogue is None else epilogue
+        per_block = max(1, min(rows, self.FEW_SMEM_FLOATS // K)) if rows <= self.FEW and K <= self.FEW_MAX_K else 0
+        ax = aux or (None, 0, None, 0, 0)
+        api.gemm_seq_f32(x_ptr, ldx, a_batch, self.weight.device_ptr, self.wdt, N * K if batch > 1 else 0, out_ptr, ldo, c_batch,
+                         rows, N, K, batch, epi, self.scale if p0 is None else p0, self.cap if p1 is None else p1, col_scale,
+                         ax[0], ax[1], ax[2], ax[3], ax[4], per_block, _st())
 
     def forward_grouped(self, x_ptr: int, ldx: int, out_ptr: int, ldo: int, a_rows: int | None, group_off: int,
                         max_rows: int) -> None:

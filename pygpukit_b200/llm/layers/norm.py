@@ -25,4 +25,35 @@ class Norm:
         return layernorm(x, self.weight, self.bias, self.eps, out=out)
 
 
-__all__ = ["Norm"]
+class RowNorm:
+    """Norm of float32 rows in the token-major models: "layernorm" (weight, bias) or an RMS norm whose weight enters as
+    (offset + weight) -- offset 1 for weights stored around zero, 0 for plain ones.  `forward` can gather its rows
+    (final norm of the wanted rows), add a second summand first and write the sum back (the start of a loop pass), or
+    accumulate into the output (a normalised branch added to the residual stream)."""
+
+    def __init__(self, kind: str, weight: GPUArray, bias: GPUArray | None = None, eps: float = 1e-5, offset: float = 0.0):
+        if kind not in ("layernorm", "rmsnorm"):
+            raise ValueError(f"RowNorm: unknown kind {kind!r}")
+        if kind == "layernorm" and bias is None:
+            raise ValueError("RowNorm: LayerNorm requires a bias")
+        self.kind, self.weight, self.bias, self.eps, self.offset = kind, weight, bias, float(eps), float(offset)
+
+    @property
+    def nbytes(self) -> int:
+        return self.weight.nbytes + (self.bias.nbytes if self.bias is not None else 0)
+
+    def forward(self, x_ptr: int, out_ptr: int, rows: int, width: int, *, src_rows: int | None = None,
+                add_ptr: int | None = None, sum_out_ptr: int | None = None, accumulate: bool = False) -> None:
+        from ..._lib import api
+        from ...core.stream import current_stream_handle as _st
+        if self.kind == "rmsnorm":
+            api.rms_norm_rows_f32(x_ptr, src_rows, add_ptr, sum_out_ptr, self.weight.device_ptr, self.offset, self.eps,
+                                  out_ptr, rows, width, 1 if accumulate else 0, _st())
+            return
+        if add_ptr is not None or sum_out_ptr is not None:
+            raise ValueError("RowNorm: a LayerNorm row takes no second summand")
+        api.combine_layernorm_f32(x_ptr, src_rows, None, None, None, 0, self.weight.device_ptr, self.bias.device_ptr,
+                                  self.eps, out_ptr, rows, width, 1 if accumulate else 0, _st())
+
+
+__all__ = ["Norm", "RowNorm"]

@@ -11,6 +11,13 @@ Dolurax tensor names: embed, head, final.norm(.b); per layer l<i>.norm1(.b), l<i
 l<i>.mix.{q,k}.norm, l<i>.mix.vmix (scalar), l<i>.mlp.router, l<i>.mlp.e<j>.{gate,up,down},
 l<i>.mlp.shared.{gate,up,down}; linear weights [out, in].  q, k, v and the gate are fused row-wise into one
 projection, gate/up pairs are interleaved row by row for the SiLU-multiply epilogue, experts are stacked.
+
+Turutar tensor names: embed, embed.norm, side.embed [vocab, layers x side dim], final.norm, head; per layer l<i>.norm1,
+l<i>.ls1, l<i>.ls2, l<i>.mlp.{gate,up,down}, l<i>.side.{gate,proj,norm}; windowed attention l<i>.mix.{q,k} with biases
+.q.b / .k.b and whole-projection norm weights .q.norm / .k.norm, l<i>.mix.g [heads, width], l<i>.mix.o; latent attention
+l<i>.mix.{dq,uq,dkv,uk,uv,g,o}, .dq.norm, .dkv.norm, .sink.  The projections that read the block's normed rows are fused
+row-wise ([q | k | g] and [dq | dkv | g]); uk is stored per head transposed ([heads, kv_rank, dim]) so that the query
+absorbs it, uv as the stack [heads, vdim, kv_rank].
 """
 from __future__ import annotations
 
@@ -23,10 +30,14 @@ from ..core.array import GPUArray
 from ..core.dtypes import bf16_bits_to_f32, f32_to_bf16_bits
 from ..core.factory import from_numpy
 from .config import LayeredConfig, layered_config_from_json
-from .layers.block import PostNormBlock
+from .layers.block import ParallelBlock, PostNormBlock
+from .layers.dense_rows import GatedDenseRows
+from .layers.latent_attention import LatentAttentionMixer
 from .layers.linear import LinearRows, interleave_gate_up
 from .layers.moe_rows import GroupedRouterMoE
+from .layers.norm import RowNorm
 from .layers.paged_attention import PagedAttentionMixer
+from .layers.token_side import TokenSideInput
 from .models.layered import LayeredCausalModel
 from .safetensors import load_safetensors
 
@@ -68,6 +79,61 @@ def build_layered_model(config: LayeredConfig, tensors, dtype: str = "bfloat16")
     if dtype not in ("bfloat16", "float32"):
         raise ValueError("layered models run in 'bfloat16' or 'float32'")
     t = tensors if isinstance(tensors, _Tensors) else _Tensors(tensors)
+    builder = _BUILDERS.get(config.architecture.lower())
+    if builder is None:
+        raise ValueError(f"no weight layout known for architecture {config.architecture!r}")
+    return builder(config, t, dtype)
+
+
+def _build_turutar(config: LayeredConfig, t: _Tensors, dtype: str) -> LayeredCausalModel:
+    W, V, eps, sd = config.hidden_size, config.vocab_size, config.norm_eps, config.side_dim
+    n_layers = len(config.layers)
+
+    def norm1p(name):                      # the model's norm: weights stored around zero
+        return RowNorm("rmsnorm", _vector(t.f32(name, (W,))), None, eps, offset=1.0)
+
+    side_table = _matrix(t.f32("side.embed", (V, n_layers * sd)), dtype) if sd else None
+    blocks = []
+    for i, L in enumerate(config.layers):
+        p, m = f"l{i}.", L.mixer
+        mp = p + "mix."
+        if m.kind == "attention":
+            qd, kd = m.heads * m.dim, m.kv_heads * m.dim
+            fused = np.concatenate([t.f32(mp + "q", (qd, W)), t.f32(mp + "k", (kd, W)), t.f32(mp + "g", (m.heads, W))])
+            mixer = PagedAttentionMixer(m, i, LinearRows(_matrix(fused, dtype)),
+                                        LinearRows(_matrix(t.f32(mp + "o", (W, m.heads * m.vdim)), dtype)),
+                                        _vector(t.f32(mp + "q.norm", (qd,))), _vector(t.f32(mp + "k.norm", (kd,))), eps,
+                                        q_bias=_vector(t.f32(mp + "q.b", (qd,))), k_bias=_vector(t.f32(mp + "k.b", (kd,))))
+        else:
+            hd = m.dim + m.rot_dim
+            fused = np.concatenate([t.f32(mp + "dq", (m.q_rank, W)), t.f32(mp + "dkv", (m.kv_rank + m.rot_dim, W)),
+                                    t.f32(mp + "g", (m.heads, W))])
+            uk = t.f32(mp + "uk", (m.heads * m.dim, m.kv_rank)).reshape(m.heads, m.dim, m.kv_rank).transpose(0, 2, 1)
+            uv = t.f32(mp + "uv", (m.heads * m.vdim, m.kv_rank)).reshape(m.heads, m.vdim, m.kv_rank)
+            mixer = LatentAttentionMixer(m, i, LinearRows(_matrix(fused, dtype)),
+                                         LinearRows(_matrix(t.f32(mp + "uq", (m.heads * hd, m.q_rank)), dtype)),
+                                         LinearRows(_matrix(uk, dtype)), LinearRows(_matrix(uv, dtype)),
+                                         LinearRows(_matrix(t.f32(mp + "o", (W, m.heads * m.vdim)), dtype)),
+                                         _vector(t.f32(mp + "dq.norm", (m.q_rank,))), _vector(t.f32(mp + "dkv.norm", (m.kv_rank,))),
+                                         eps, sinks=_vector(t.f32(mp + "sink", (m.heads,))))
+        mlp = ls2 = None
+        if L.mlp is not None:
+            f, q = L.mlp, p + "mlp."
+            gu = interleave_gate_up(t.f32(q + "gate", (f.ff, W)), t.f32(q + "up", (f.ff, W)))
+            mlp = GatedDenseRows(f, LinearRows(_matrix(gu, dtype)), LinearRows(_matrix(t.f32(q + "down", (W, f.ff)), dtype)))
+            ls2 = _vector(t.f32(p + "ls2", (W,)))
+        side = None
+        if sd:
+            side = TokenSideInput(side_table, i, sd, LinearRows(_matrix(t.f32(p + "side.gate", (sd, W)), dtype)),
+                                  LinearRows(_matrix(t.f32(p + "side.proj", (W, sd)), dtype)),
+                                  RowNorm("rmsnorm", _vector(t.f32(p + "side.norm", (W,))), None, eps, offset=0.0))
+        blocks.append(ParallelBlock(norm1p(p + "norm1"), mixer, _vector(t.f32(p + "ls1", (W,))), mlp, ls2, side))
+    head = LinearRows(_matrix(t.f32("head", (V, W)), dtype))
+    return LayeredCausalModel(config, _matrix(t.f32("embed", (V, W)), dtype), blocks, norm1p("final.norm"), head, dtype,
+                              embed_norm=norm1p("embed.norm"))
+
+
+def _build_dolurax(config: LayeredConfig, t: _Tensors, dtype: str) -> LayeredCausalModel:
     W, V, eps = config.hidden_size, config.vocab_size, config.norm_eps
     blocks = []
     first_mix = None          # index and value width of the first value-mixing layer
@@ -111,6 +177,10 @@ def build_layered_model(config: LayeredConfig, tensors, dtype: str = "bfloat16")
     head = LinearRows(_matrix(t.f32("head", (V, W)), dtype), epilogue=2, scale=config.logit_scale, cap=config.logit_softcap)
     final = (_vector(t.f32("final.norm", (W,))), _vector(t.f32("final.norm.b", (W,))))
     return LayeredCausalModel(config, _matrix(t.f32("embed", (V, W)), dtype), blocks, final, head, dtype)
+
+
+# architecture (lower case) -> builder of its blocks from the checkpoint's tensors
+_BUILDERS = {"dolurax": _build_dolurax, "turutar": _build_turutar}
 
 
 def load_layered_model(model_path: str, dtype: str = "bfloat16", config: dict | None = None) -> LayeredCausalModel:

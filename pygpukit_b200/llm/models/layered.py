@@ -25,8 +25,8 @@ from ...core.dtypes import float32, int32
 from ...core.stream import CudaGraph, Stream, current_stream_handle as _st
 from ..buffers import RowBuffers
 from ..config import LayeredConfig
-from ..layers.block import PostNormBlock
 from ..layers.linear import LinearRows
+from ..layers.norm import RowNorm
 from ..paged_cache import PagedKVCache
 
 
@@ -86,9 +86,10 @@ class StepContext:
         self.cache = cache
         self.buf = model._buffers(self.T)
 
-    def max_keys(self, chunk: int) -> int:
-        """The longest key range any sequence of the step reads under a chunk size (0: none)."""
-        return max(p0 + n - ((p0 // chunk) * chunk if chunk > 0 else 0) for _, n, _, p0 in self._seqs)
+    def max_keys(self, chunk: int, window: int = 0) -> int:
+        """The longest key range any tile of the step reads under a chunk size and a window (0: none)."""
+        keys = max(p0 + n - ((p0 // chunk) * chunk if chunk > 0 else 0) for _, n, _, p0 in self._seqs)
+        return min(keys, window + 64) if window > 0 else keys
 
     def workspace(self, n_floats: int) -> GPUArray:
         return self._model._workspace(n_floats)
@@ -104,10 +105,19 @@ class StepContext:
 
 
 class LayeredCausalModel:
-    def __init__(self, config: LayeredConfig, embed_tokens: GPUArray, blocks: list[PostNormBlock],
-                 final_norm: tuple[GPUArray, GPUArray], lm_head: LinearRows, dtype: str = "bfloat16"):
+    def __init__(self, config: LayeredConfig, embed_tokens: GPUArray, blocks: list, final_norm, lm_head: LinearRows,
+                 dtype: str = "bfloat16", embed_norm: RowNorm | None = None):
+        """blocks: one PostNormBlock / ParallelBlock per layer of the config; final_norm: a RowNorm, or the (weight, bias)
+        pair of a LayerNorm; embed_norm: the norm applied to the embedding rows (configs with `embed_norm`)."""
         self.config, self.embed_tokens, self.blocks = config, embed_tokens, blocks
+        if isinstance(final_norm, tuple):
+            final_norm = RowNorm("layernorm", final_norm[0], final_norm[1], config.norm_eps)
         self.final_norm, self.lm_head, self.dtype = final_norm, lm_head, dtype
+        self.embed_norm = embed_norm
+        if bool(config.embed_norm) != (embed_norm is not None):
+            raise ValueError("LayeredCausalModel: the config and the embedding norm do not agree")
+        self.runs = config.layer_runs()                 # (layer, add the embedding output first); index = cache
+        self.trace_hook = None                          # debugging aid: called with (run index, residual rows array)
         self.embed_dt = 2 if embed_tokens.dtype.name == "bfloat16" else 0
         self.cache: PagedKVCache | None = None
         self._buf: RowBuffers | None = None
@@ -119,12 +129,12 @@ class LayeredCausalModel:
         self._graph_warm: set = set()
         self._gstream: Stream | None = None
         self._tile_sizes = {b.mixer.queries_per_tile for b in blocks}
-        self._tops = {b.mlp.spec.top for b in blocks if b.mlp is not None}
+        self._tops = {b.mlp.spec.top for b in blocks if b.mlp is not None and b.mlp.spec.kind == "moe"}
 
     # ------------------------------------------------------------------ setup
     def init_cache(self, max_tokens: int = 4096, page_size: int = 64, slots: int = 8) -> PagedKVCache:
         """Allocate the paged cache for about `max_tokens` live positions (it grows when more arrive)."""
-        shapes = [(b.mixer.spec.kv_heads, b.mixer.spec.dim, b.mixer.spec.vdim) for b in self.blocks]
+        shapes = [self.blocks[li].mixer.spec.cache_shape() for li, _ in self.runs]
         self.cache = PagedKVCache(shapes, self.dtype, page_size, max_tokens, slots)
         self._graphs.clear()
         self._graph_warm.clear()
@@ -153,13 +163,18 @@ class LayeredCausalModel:
         b, T = ctx.buf, ctx.T
         x = b.x
         api.embed_rows_f32(self.embed_tokens.device_ptr, self.embed_dt, ctx.tok_ptr, x.device_ptr, T, W, V, _st())
-        for blk in self.blocks:
-            blk.forward(ctx, x)
+        if self.embed_norm is not None:
+            self.embed_norm.forward(x.device_ptr, x.device_ptr, T, W)
+        if b.x0 is not None:                           # kept for the later passes of the loop
+            api.memcpy_d2d(b.x0.device_ptr, x.device_ptr, T * W * 4, _st())
+        for run, (li, add_first) in enumerate(self.runs):
+            self.blocks[li].forward(ctx, x, run, b.x0.device_ptr if add_first else None)
+            if self.trace_hook is not None:
+                self.trace_hook(run, x.to_numpy()[:T].copy())
         if ctx.n_want:
             n = ctx.n_want
             xn = b.y                                   # free after the last block
-            api.combine_layernorm_f32(x.device_ptr, ctx.want_ptr, None, None, None, 0, self.final_norm[0].device_ptr,
-                                      self.final_norm[1].device_ptr, cfg.norm_eps, xn.device_ptr, n, W, 0, _st())
+            self.final_norm.forward(x.device_ptr, xn.device_ptr, n, W, src_rows=ctx.want_ptr)
             self.lm_head.forward(xn.device_ptr, W, n, self._out.device_ptr, V)
 
     def _graph_key(self, ctx: StepContext):
@@ -246,7 +261,7 @@ class LayeredCausalModel:
 
     # ------------------------------------------------------------------ accounting
     def weight_bytes_per_token(self) -> int:
-        return sum(b.weight_bytes for b in self.blocks) + self.lm_head.nbytes
+        return sum(self.blocks[li].weight_bytes for li, _ in self.runs) + self.lm_head.nbytes
 
 
 __all__ = ["LayeredCausalModel", "StepContext"]

@@ -124,7 +124,9 @@ class PagePool:
 
 
 class PagedKVCache:
-    """Device arrays of every layer + the page pool.  `layer_shapes` = [(kv_heads, dim, vdim), ...]."""
+    """Device arrays of every layer + the page pool.  `layer_shapes` = [(kv_heads, dim, vdim), ...], one entry per cache
+    (a layer that runs several times in a loop has one per run); vdim 0: the layer keeps one array whose rows serve as
+    keys and, by a prefix, as values (latent attention) -- `v[i]` is then None."""
 
     def __init__(self, layer_shapes: list[tuple[int, int, int]], dtype: str = "bfloat16", page_size: int = 64,
                  tokens_hint: int = 4096, slots: int = 8):
@@ -136,7 +138,7 @@ class PagedKVCache:
         pages = -(-max(1, tokens_hint) // page_size) + slots          # every live sequence may hold one partial page
         self.pool = PagePool(page_size, pages, slots, max(4, -(-max(1, tokens_hint) // page_size) + 1))
         self.k: list[GPUArray] = []
-        self.v: list[GPUArray] = []
+        self.v: list[GPUArray | None] = []
         self._alloc(pages, copy_from=None)
         self.table_dev = zeros((self.pool.slots * self.pool.max_pages,), int32)
 
@@ -148,10 +150,12 @@ class PagedKVCache:
         ps = self.pool.page_size
         k_new, v_new = [], []
         for i, (g, d, dv) in enumerate(self.layer_shapes):
-            k, v = zeros((pages, g, ps, d), self.dtype), zeros((pages, g, ps, dv), self.dtype)
+            k = zeros((pages, g, ps, d), self.dtype)
+            v = zeros((pages, g, ps, dv), self.dtype) if dv > 0 else None
             if copy_from is not None:
                 api.memcpy_d2d(k.device_ptr, self.k[i].device_ptr, self.k[i].nbytes, _st())
-                api.memcpy_d2d(v.device_ptr, self.v[i].device_ptr, self.v[i].nbytes, _st())
+                if v is not None:
+                    api.memcpy_d2d(v.device_ptr, self.v[i].device_ptr, self.v[i].nbytes, _st())
             k_new.append(k)
             v_new.append(v)
         if copy_from is not None:
@@ -183,7 +187,7 @@ class PagedKVCache:
 
     @property
     def nbytes(self) -> int:
-        return sum(a.nbytes for a in self.k) + sum(a.nbytes for a in self.v)
+        return sum(a.nbytes for a in self.k) + sum(a.nbytes for a in self.v if a is not None)
 
 
 __all__ = ["PagePool", "PagedKVCache"]
