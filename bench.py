@@ -35,6 +35,10 @@ N > 1 (torchrun): tensor-parallel over N GPUs (strong scaling: the same token st
     python bench.py --layered [--layered-sizes a3b-2048,moe-4096] [--steps K] [--warmup W]
 An option beside the default workload (whose contract is unchanged): prompt and decode throughput of the layered
 (Dolurax) family at real layer sizes next to Qwen3-MoE at equal sizes, one JSON line (scripts/bench_layered.py).
+
+    python bench.py --turutar [--turutar-sizes t-2048,t-4096] [--steps K] [--warmup W]
+The same for the Turutar design (latent + windowed attention, gated dense feed-forward, token side inputs, a looped pair of
+layers) next to a Dolurax stack of equal size, the closest existing model: same family, same cache and kernels.
 """
 from __future__ import annotations
 
@@ -82,6 +86,10 @@ def parse_args():
                     help="instead of the default workload: prefill / decode throughput of the layered (Dolurax) family at "
                          "real layer sizes beside Qwen3-MoE at equal sizes (scripts/bench_layered.py), one JSON line")
     ap.add_argument("--layered-sizes", default="a3b-2048,moe-4096")
+    ap.add_argument("--turutar", action="store_true",
+                    help="instead of the default workload: prefill / decode throughput of the Turutar design (latent + windowed "
+                         "attention, dense feed-forward, layer loop) beside a Dolurax stack of equal size, one JSON line")
+    ap.add_argument("--turutar-sizes", default="t-2048,t-4096")
     return ap.parse_args()
 
 
@@ -607,6 +615,11 @@ def run_ours(args) -> None:
 
 def main():
     args = parse_args()
+    if args.turutar:
+        sys.path.insert(0, os.path.join(ROOT, "scripts"))
+        import bench_layered
+        print(json.dumps(bench_layered.main_turutar(ROOT, args.turutar_sizes.split(","), args.steps, args.warmup)))
+        return
     if args.layered:
         sys.path.insert(0, os.path.join(ROOT, "scripts"))
         import bench_layered

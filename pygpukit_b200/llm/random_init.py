@@ -309,6 +309,8 @@ def random_layered_model(config, dtype: str = "bfloat16", seed: int = 1234, std:
     def vec(size, value):
         return from_numpy(np.full((size,), value, np.float32))
 
+    if config.block == "parallel":
+        return _random_parallel_model(config, dtype, mat, vec)
     blocks, mixing = [], False
     for i, L in enumerate(config.layers):
         m = L.mixer
@@ -328,3 +330,47 @@ def random_layered_model(config, dtype: str = "bfloat16", seed: int = 1234, std:
         blocks.append(PostNormBlock(mixer, (vec(W, 1.0), vec(W, 0.0)), mlp, norm2, eps))
     head = LinearRows(mat(V, W), epilogue=2, scale=config.logit_scale, cap=config.logit_softcap)
     return LayeredCausalModel(config, mat(V, W), blocks, (vec(W, 1.0), vec(W, 0.0)), head, dtype)
+
+
+def _random_parallel_model(config, dtype, mat, vec):
+    """The parallel-block form of `random_layered_model` (windowed / latent attention, gated dense feed-forward, token
+    side inputs): random matrices, norms at identity, unit layer scales, zero biases and sinks."""
+    from .layers.block import ParallelBlock
+    from .layers.dense_rows import GatedDenseRows
+    from .layers.latent_attention import LatentAttentionMixer
+    from .layers.linear import LinearRows
+    from .layers.norm import RowNorm
+    from .layers.paged_attention import PagedAttentionMixer
+    from .layers.token_side import TokenSideInput
+    from .models.layered import LayeredCausalModel
+    W, V, eps, sd = config.hidden_size, config.vocab_size, config.norm_eps, config.side_dim
+    off = 1.0 if config.norm == "rmsnorm_1p" else 0.0
+
+    def norm():
+        return RowNorm("rmsnorm", vec(W, 1.0 - off), None, eps, offset=off)
+
+    table = mat(V, len(config.layers) * sd) if sd else None
+    blocks = []
+    for i, L in enumerate(config.layers):
+        m = L.mixer
+        if m.kind == "attention":
+            qd, kd = m.heads * m.dim, m.kv_heads * m.dim
+            mixer = PagedAttentionMixer(m, i, LinearRows(mat(m.proj_cols, W)), LinearRows(mat(W, m.heads * m.vdim)), vec(qd, 1.0),
+                                        vec(kd, 1.0), eps, q_bias=vec(qd, 0.0) if m.qk_bias else None,
+                                        k_bias=vec(kd, 0.0) if m.qk_bias else None,
+                                        sinks=vec(m.heads, 0.0) if m.sink == "learned" else None)
+        else:
+            mixer = LatentAttentionMixer(m, i, LinearRows(mat(m.proj_cols, W)), LinearRows(mat(m.heads * (m.dim + m.rot_dim), m.q_rank)),
+                                         LinearRows(mat(m.heads, m.kv_rank, m.dim)), LinearRows(mat(m.heads, m.vdim, m.kv_rank)),
+                                         LinearRows(mat(W, m.heads * m.vdim)), vec(m.q_rank, 1.0), vec(m.kv_rank, 1.0), eps,
+                                         sinks=vec(m.heads, 0.0) if m.sink == "learned" else None)
+        mlp = None
+        if L.mlp is not None:
+            mlp = GatedDenseRows(L.mlp, LinearRows(mat(2 * L.mlp.ff, W)), LinearRows(mat(W, L.mlp.ff)))
+        side = None
+        if sd:
+            side = TokenSideInput(table, i, sd, LinearRows(mat(sd, W)), LinearRows(mat(W, sd)),
+                                  RowNorm("rmsnorm", vec(W, 1.0), None, eps, offset=0.0))
+        blocks.append(ParallelBlock(norm(), mixer, vec(W, 1.0), mlp, vec(W, 1.0) if mlp is not None else None, side))
+    return LayeredCausalModel(config, mat(V, W), blocks, norm(), LinearRows(mat(V, W)), dtype,
+                              embed_norm=norm() if config.embed_norm else None)

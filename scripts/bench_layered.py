@@ -29,6 +29,16 @@ SIZES = {
 }
 
 
+# Turutar: parallel blocks of latent attention (one cached row of kv_rank + rot per position) and windowed attention whose
+# values are its keys, gated dense feed-forward, token side input; the two layers run twice (loop), i.e. four layer runs
+TURUTAR_SIZES = {
+    "t-2048": dict(width=2048, heads=16, kv_heads=4, dim=128, window=1024, ldim=128, rot=64, lvdim=128, kv_rank=512, q_rank=768,
+                   ff=8192, side=256, times=2, vocab=32768),
+    "t-4096": dict(width=4096, heads=32, kv_heads=8, dim=128, window=2048, ldim=128, rot=64, lvdim=128, kv_rank=512, q_rank=1536,
+                   ff=12288, side=256, times=2, vocab=32768),
+}
+
+
 def peaks(root: str) -> tuple[float, float, str]:
     p = os.path.join(root, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -49,6 +59,57 @@ def layered_config(s: dict):
                                                                             for _ in range(s["layers"])],
                                      "logit_scale": 1.0, "logit_softcap": 30.0, "norm": {"eps": 1e-5}, "vocab": s["vocab"],
                                      "width": s["width"]})
+
+
+def turutar_config(s: dict):
+    from pygpukit_b200.llm.config import layered_config_from_json
+    mlp = {"kind": "dense", "ff": s["ff"], "limit": 7.0}
+    latent = {"type": "latent_attention", "mlp": mlp,
+              "mixer": {"heads": s["heads"], "dim": s["ldim"], "rot_dim": s["rot"], "vdim": s["lvdim"], "kv_rank": s["kv_rank"],
+                        "q_rank": s["q_rank"], "scale": (s["ldim"] + s["rot"]) ** -0.5, "rot": {"dims": s["rot"], "base": 10000.0}}}
+    windowed = {"type": "attention", "mlp": mlp,
+                "mixer": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5,
+                          "mask": {"size": s["window"]}}}
+    return layered_config_from_json({"architecture": "Turutar", "layers": [latent, windowed], "loop": {"start": 0, "stop": 2, "times": s["times"]},
+                                     "norm": {"eps": 1e-6}, "token_side": {"dim": s["side"]}, "vocab": s["vocab"], "width": s["width"]})
+
+
+def dense_twin_config(s: dict):
+    """The closest existing model at equal size: as many Dolurax layers as Turutar layer runs, attention with the windowed
+    mixer's heads and a chunk of the window's size, one expert of the same feed-forward size (top 1), no shared expert."""
+    from pygpukit_b200.llm.config import layered_config_from_json
+    mixer = {"dim": s["dim"], "heads": s["heads"], "kv_heads": s["kv_heads"], "mask": {"size": s["window"]},
+             "scale": s["dim"] ** -0.5, "softcap": 50.0, "v_mix": False, "vdim": s["dim"]}
+    mlp = {"expert": {"ff": s["ff"]}, "kind": "moe", "router": {"experts": 1, "groups": {"count": 1, "keep": 1}, "top": 1}, "shared": None}
+    return layered_config_from_json({"architecture": "Dolurax", "layers": [{"type": "attention", "mixer": mixer, "mlp": mlp}
+                                                                            for _ in range(2 * s["times"])],
+                                     "logit_scale": 1.0, "logit_softcap": 0.0, "norm": {"eps": 1e-5}, "vocab": s["vocab"], "width": s["width"]})
+
+
+def turutar_bytes_flops(s: dict, T: int, B: int, ctx: int) -> tuple[float, float]:
+    """(bytes a decode step of B tokens touches, FLOPs of a T-token prefill) over the 2 x times layer runs"""
+    W, H, G, D = s["width"], s["heads"], s["kv_heads"], s["dim"]
+    R, rot, hd = s["kv_rank"], s["rot"], s["ldim"] + s["rot"]
+    ff_w = 3 * s["ff"] * W + 2 * s["side"] * W
+    win_w = (H * D + G * D + H) * W + W * H * D
+    lat_w = (s["q_rank"] + R + rot + H) * W + H * hd * s["q_rank"] + H * s["ldim"] * R + H * s["lvdim"] * R + W * H * s["lvdim"]
+    seen_w = min(ctx, s["window"])
+    dec = s["times"] * (2 * (win_w + lat_w + 2 * ff_w) + B * 2 * (2 * G * seen_w * D + ctx * (R + rot))) + 2 * s["vocab"] * W
+    seen_avg = min(T, s["window"]) / 2 if T <= s["window"] else s["window"] * (1 - s["window"] / (2 * T))
+    attn_fl = 2 * T * H * seen_avg * 2 * D + 2 * T * H * (T / 2) * (2 * R + rot)
+    fl = s["times"] * (2 * T * (win_w + lat_w + 2 * ff_w) + attn_fl) + 2 * s["vocab"] * W
+    return float(dec), float(fl)
+
+
+def twin_bytes_flops(s: dict, T: int, B: int, ctx: int) -> tuple[float, float]:
+    W, H, G, D = s["width"], s["heads"], s["kv_heads"], s["dim"]
+    layer_w = (H * D + 2 * G * D + H * D) * W + W * H * D + W + 3 * s["ff"] * W
+    seen = min(ctx, s["window"])
+    n = 2 * s["times"]
+    dec = n * (2 * layer_w + B * 2 * 2 * G * seen * D) + 2 * s["vocab"] * W
+    seen_avg = min(T, s["window"]) / 2
+    fl = n * (2 * T * layer_w + 2 * T * H * seen_avg * 2 * D) + 2 * s["vocab"] * W
+    return float(dec), float(fl)
 
 
 def _timed(fn, iters: int, warm: int) -> float:
@@ -84,9 +145,14 @@ def dolurax_bytes_flops(s: dict, T: int, B: int, ctx: int) -> tuple[float, float
 
 
 def run_dolurax(s: dict, prompt: int, decode_batches, steps: int, warm: int, hbm: float, tflops: float) -> dict:
+    return run_layered(layered_config(s), lambda T, B, ctx: dolurax_bytes_flops(s, T, B, ctx), s["vocab"], prompt, decode_batches,
+                       steps, warm, hbm, tflops)
+
+
+def run_layered(cfg, bytes_flops, vocab: int, prompt: int, decode_batches, steps: int, warm: int, hbm: float, tflops: float) -> dict:
     from pygpukit_b200 import llm
     from pygpukit_b200._lib import api, load
-    cfg = layered_config(s)
+    s = {"vocab": vocab}
     t0 = time.perf_counter()
     model = llm.random_layered_model(cfg)
     model.init_cache(max_tokens=prompt * (max(decode_batches) + 1) + 4096, page_size=64, slots=16)
@@ -105,7 +171,7 @@ def run_dolurax(s: dict, prompt: int, decode_batches, steps: int, warm: int, hbm
     prefill()
     out["prefill_launches"] = int(lib.pgk_launch_count())
     ms = _timed(prefill, max(3, steps // 8), 2)
-    _, fl = dolurax_bytes_flops(s, prompt, 1, prompt)
+    _, fl = bytes_flops(prompt, 1, prompt)
     out["prefill"] = {"tokens": prompt, "ms": round(ms, 3), "tokens_per_s": round(prompt / ms * 1e3, 1),
                       "tflops": round(fl / ms / 1e9, 2), "frac_of_bf16_peak": round(fl / ms / 1e9 / tflops, 4)}
     out["decode"] = {}
@@ -121,7 +187,7 @@ def run_dolurax(s: dict, prompt: int, decode_batches, steps: int, warm: int, hbm
         dec()
         launches = int(lib.pgk_launch_count())
         ms = _timed(dec, steps, warm)
-        by, _ = dolurax_bytes_flops(s, 1, B, prompt)
+        by, _ = bytes_flops(1, B, prompt)
         out["decode"][f"b{B}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(B / ms * 1e3, 1), "launches": launches,
                                   "bytes_per_step": by, "gbs": round(by / ms / 1e6, 1), "frac_of_hbm_peak": round(by / ms / 1e6 / hbm, 4)}
         for i in ids:
@@ -175,6 +241,26 @@ def run_qwen3_moe(s: dict, prompt: int, decode_batches, steps: int, warm: int, h
         out["decode"][f"b{B}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(B / ms * 1e3, 1), "bytes_per_step": float(by),
                                   "gbs": round(by / ms / 1e6, 1), "frac_of_hbm_peak": round(by / ms / 1e6 / hbm, 4)}
     return out
+
+
+def main_turutar(root: str, sizes: list[str], steps: int, warm: int, prompt: int = 2000) -> dict:
+    """Turutar beside its dense twin of the same family at equal size: prefill of `prompt` tokens, decode of 1 and 8
+    requests at that context."""
+    from pygpukit_b200._lib import api
+    hbm, tflops, src = peaks(root)
+    res = {"metric": "turutar_prefill_decode_tokens_per_s", "data": "synthetic", "dtype": "bf16 matrices and cache, f32 residual / norms / softmax",
+           "peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": src}, "prompt": prompt, "steps": steps, "warmup": warm, "sizes": {}}
+    for name in sizes:
+        s = TURUTAR_SIZES[name]
+        entry = {"shape": dict(s)}
+        entry["turutar"] = run_layered(turutar_config(s), lambda T, B, ctx: turutar_bytes_flops(s, T, B, ctx), s["vocab"], prompt,
+                                       (1, 8), steps, max(3, warm), hbm, tflops)
+        api.device_sync()
+        entry["dolurax_dense_twin"] = run_layered(dense_twin_config(s), lambda T, B, ctx: twin_bytes_flops(s, T, B, ctx), s["vocab"],
+                                                  prompt, (1, 8), steps, max(3, warm), hbm, tflops)
+        api.device_sync()
+        res["sizes"][name] = entry
+    return res
 
 
 def main(root: str, sizes: list[str], steps: int, warm: int, prompt: int = 2000) -> dict:
