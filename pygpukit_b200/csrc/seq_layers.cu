@@ -239,7 +239,7 @@ int pgk_combine_layernorm_f32(const float* base, const int32_t* src_rows, const 
     NormArgs a{base, src_rows, parts, inv, weights, top, gamma, beta, eps, out, width, add};
     const size_t smem = (size_t)width * 4;
     static bool configured = false;
-    if (smem > 48 * 1024 && !configured) {
+    if (smem > 40 * 1024 && !configured) {          // dynamic + static shared memory pass 48 KB a little earlier
         PGK_CUDA(cudaFuncSetAttribute(combine_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
         configured = true;
     }
@@ -255,7 +255,7 @@ int pgk_rms_norm_rows_f32(const float* x, const int32_t* src_rows, const float* 
     RmsArgs a{x, src_rows, add, sum_out, weight, weight_offset, eps, out, width, accumulate};
     const size_t smem = (size_t)width * 4;
     static bool configured = false;
-    if (smem > 48 * 1024 && !configured) {
+    if (smem > 40 * 1024 && !configured) {          // dynamic + static shared memory pass 48 KB a little earlier
         PGK_CUDA(cudaFuncSetAttribute(rms_norm_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
         configured = true;
     }

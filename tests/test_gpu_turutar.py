@@ -183,7 +183,7 @@ class WindowHarness:
 
 
 @pytest.mark.parametrize("H,G,D,window,page", [(4, 1, 16, 6, 4), (4, 2, 8, 1, 3), (3, 3, 12, 100, 4), (8, 2, 32, 17, 8),
-                                               (2, 1, 20, 9, 5), (40, 1, 8, 5, 4), (1, 1, 6, 0, 4)])
+                                               (2, 1, 20, 9, 5), (40, 1, 8, 5, 4), (1, 1, 6, 0, 4), (2, 1, 112, 11, 8)])
 def test_windowed_attention_whole_portions_and_single_tokens_agree_with_the_oracle(H, G, D, window, page):
     rng = np.random.default_rng(H * 7 + D)
     T = 45
@@ -201,6 +201,8 @@ def test_windowed_attention_whole_portions_and_single_tokens_agree_with_the_orac
     h.decode_kernel = False                                              # the same through the tile kernel
     single = np.concatenate([h.run("t", q[i:i + 1], k[i:i + 1], gate[i:i + 1]) for i in range(T)])
     assert np.abs(single - ref).max() < 1e-5
+    # (the layout with heads of 112, like the latent one with rows of 160, needs 40-48 KB of dynamic shared memory: together
+    # with the kernels' static arrays that is past the limit a launch may use without opting in)
 
 
 @pytest.mark.parametrize("decoded", [False, True])
@@ -314,7 +316,7 @@ class LatentHarness:
 
 
 @pytest.mark.parametrize("H,nc,Dr,dims,page", [(3, 20, 12, 12, 4), (6, 40, 6, 4, 3), (2, 264, 8, 8, 8), (33, 8, 4, 4, 4),
-                                               (1, 30, 0, 0, 5)])
+                                               (1, 30, 0, 0, 5), (4, 128, 32, 32, 8)])
 def test_latent_attention_whole_portions_and_single_tokens_agree_with_the_oracle(H, nc, Dr, dims, page):
     rng = np.random.default_rng(H + nc)
     T = 45
