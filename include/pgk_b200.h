@@ -557,6 +557,13 @@ int pgk_seq_rope_heads(const float* src, int lds, int src_head, int src_off, flo
  * + eps) * (weight_offset + weight); accumulate != 0: out[t] += r, else out[t] = r.  out may be x. */
 int pgk_rms_norm_rows_f32(const float* x, const int32_t* src_rows, const float* add, float* sum_out, const float* weight,
                           float weight_offset, float eps, float* out, int rows, int width, int accumulate, void* stream);
+/* The seam between two pre-norm blocks in one pass over the row: x[t] += rms(y[t]) * (offset1 + weight1); then, with add
+ * (or NULL) added and written back into x too, h[t] = rms(x[t]) * (offset2 + weight2). */
+int pgk_rms_norm_seam_f32(const float* y, const float* weight1, float offset1, float* x, const float* add, const float* weight2,
+                          float offset2, float eps, float* h, int rows, int width, void* stream);
+/* x[t] = rms(table[tokens[t]]) * (weight_offset + weight), written to keep[t] as well when keep is not NULL */
+int pgk_embed_norm_rows_f32(const void* table, int wdt, const int32_t* tokens, const float* weight, float weight_offset, float eps,
+                            float* x, float* keep, int n, int width, int vocab, void* stream);
 /* The general row GEMM: `batch` products over the same M rows, product b reading A columns from b * a_batch, matrix
  * W + b * w_batch and writing C columns from b * c_batch (one product per attention head).  Epilogues 0-2 as above with
  * p0 = scale, p1 = cap; 3: gate/up pairs, g = min(gate, p1), u = clamp(up, -p1, p1), C[m, j] = g sigmoid(p0 g) (u + 1);

@@ -127,6 +127,8 @@ _SIGS = {
     "pgk_seq_latent_prep": [vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, f32, f32, vp, vp, i32, vp, i32, i32, vp, vp, vp],
     "pgk_seq_rope_heads": [vp, i32, i32, i32, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp],
     "pgk_rms_norm_rows_f32": [vp, vp, vp, vp, vp, f32, f32, vp, i32, i32, i32, vp],
+    "pgk_rms_norm_seam_f32": [vp, vp, f32, vp, vp, vp, f32, f32, vp, i32, i32, vp],
+    "pgk_embed_norm_rows_f32": [vp, i32, vp, vp, f32, f32, vp, vp, i32, i32, i32, vp],
     "pgk_gemm_seq_f32": [vp, i32, C.c_longlong, vp, i32, C.c_longlong, vp, i32, C.c_longlong, i32, i32, i32, i32, i32, f32, f32,
                          vp, vp, i32, vp, i32, i32, i32, vp],
     "pgk_seq_mixer_prep": [vp, i32, i32, i32, i32, i32, i32, vp, vp, f32, i32, f32, vp, vp, vp, i32, vp, i32, i32, vp, vp, vp],

@@ -119,6 +119,64 @@ __global__ void __launch_bounds__(256) rms_norm_rows_kernel(RmsArgs a) {
     }
 }
 
+// Two norms in one pass over the row, for the seam between two pre-norm blocks: x[t] += rms(y[t]) * (off1 + w1) (a
+// normalised branch joins the residual stream), then (+ add[t], written back into x as well) h[t] = rms(x[t]) * (off2 + w2)
+// is the next block's input.
+struct RmsSeamArgs {
+    const float* y; const float* w1; float off1;
+    float* x; const float* add;
+    const float* w2; float off2, eps;
+    float* h; int W;
+};
+
+__global__ void __launch_bounds__(256) rms_seam_kernel(RmsSeamArgs a) {
+    extern __shared__ float row[];
+    __shared__ float red[8];
+    const int t = blockIdx.x;
+    const size_t o = (size_t)t * a.W;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < a.W; i += blockDim.x) {
+        const float v = a.y[o + i];
+        row[i] = v;
+        q = fmaf(v, v, q);
+    }
+    const float inv1 = 1.f / sqrtf(block_sum256(q, red) / (float)a.W + a.eps);
+    q = 0.f;
+    for (int i = threadIdx.x; i < a.W; i += blockDim.x) {
+        float v = a.x[o + i] + row[i] * inv1 * (a.off1 + a.w1[i]);
+        if (a.add) v += a.add[o + i];
+        a.x[o + i] = v;
+        row[i] = v;
+        q = fmaf(v, v, q);
+    }
+    const float inv2 = 1.f / sqrtf(block_sum256(q, red) / (float)a.W + a.eps);
+    for (int i = threadIdx.x; i < a.W; i += blockDim.x) a.h[o + i] = row[i] * inv2 * (a.off2 + a.w2[i]);
+}
+
+// x[t] = rms(table[tokens[t]]) * (off + w), copied to keep[t] as well when given: embedding, its norm and the kept copy
+template <typename TW>
+__global__ void __launch_bounds__(256) embed_norm_rows_kernel(const TW* table, const int* tok, const float* w, float off, float eps,
+                                                              float* x, float* keep, int W, int vocab) {
+    extern __shared__ float row[];
+    __shared__ float red[8];
+    const int t = blockIdx.x;
+    int id = tok[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    const TW* src = table + (size_t)id * W;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const float v = wload<TW>(src + i);
+        row[i] = v;
+        q = fmaf(v, v, q);
+    }
+    const float inv = 1.f / sqrtf(block_sum256(q, red) / (float)W + eps);
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const float v = row[i] * inv * (off + w[i]);
+        x[(size_t)t * W + i] = v;
+        if (keep) keep[(size_t)t * W + i] = v;
+    }
+}
+
 // ---------------------------------------------------------------- router
 struct RouteArgs {
     const float* z; int ldz; int T, E, top, gcount, gkeep;
@@ -260,6 +318,38 @@ int pgk_rms_norm_rows_f32(const float* x, const int32_t* src_rows, const float* 
         configured = true;
     }
     PGK_CUDA(launch(rms_norm_rows_kernel, dim3(rows), dim3(256), smem, (cudaStream_t)stream, a));
+    return 0;
+}
+
+int pgk_rms_norm_seam_f32(const float* y, const float* weight1, float offset1, float* x, const float* add, const float* weight2,
+                          float offset2, float eps, float* h, int rows, int width, void* stream) {
+    PGK_REQUIRE(width > 0 && width * 4 <= 160 * 1024, "rms_norm_seam_f32 failed: width %d out of range", width);
+    if (rows <= 0) return 0;
+    RmsSeamArgs a{y, weight1, offset1, x, add, weight2, offset2, eps, h, width};
+    const size_t smem = (size_t)width * 4;
+    static bool configured = false;
+    if (smem > 40 * 1024 && !configured) {
+        PGK_CUDA(cudaFuncSetAttribute(rms_seam_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        configured = true;
+    }
+    PGK_CUDA(launch(rms_seam_kernel, dim3(rows), dim3(256), smem, (cudaStream_t)stream, a));
+    return 0;
+}
+
+int pgk_embed_norm_rows_f32(const void* table, int wdt, const int32_t* tokens, const float* weight, float weight_offset, float eps,
+                            float* x, float* keep, int n, int width, int vocab, void* stream) {
+    PGK_REQUIRE(wdt == 0 || wdt == 2, "embed_norm_rows_f32 failed: table must be float32 (0) or bfloat16 (2), got %d", wdt);
+    PGK_REQUIRE(width > 0 && width * 4 <= 160 * 1024, "embed_norm_rows_f32 failed: width %d out of range", width);
+    if (n <= 0) return 0;
+    const size_t smem = (size_t)width * 4;
+    static bool configured = false;
+    if (smem > 40 * 1024 && !configured) {
+        PGK_CUDA(cudaFuncSetAttribute(embed_norm_rows_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        PGK_CUDA(cudaFuncSetAttribute(embed_norm_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        configured = true;
+    }
+    if (wdt == 2) PGK_CUDA(launch(embed_norm_rows_kernel<uint16_t>, dim3(n), dim3(256), smem, (cudaStream_t)stream, (const uint16_t*)table, tokens, weight, weight_offset, eps, x, keep, width, vocab));
+    else PGK_CUDA(launch(embed_norm_rows_kernel<float>, dim3(n), dim3(256), smem, (cudaStream_t)stream, (const float*)table, tokens, weight, weight_offset, eps, x, keep, width, vocab));
     return 0;
 }
 

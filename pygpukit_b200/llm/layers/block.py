@@ -87,7 +87,10 @@ class PostNormBlock:
         self.mixer, self.mlp = mixer, mlp
         self.norm1, self.norm2, self.eps = norm1, norm2, float(eps)
 
-    def forward(self, ctx, x: GPUArray, cache_index: int | None = None, add_ptr: int | None = None) -> None:
+    norm = None                          # no norm in front of the block: nothing for the block before to fuse with
+
+    def forward(self, ctx, x: GPUArray, cache_index: int | None = None, add_ptr: int | None = None, normed: bool = False,
+                next_norm=None, next_add_ptr: int | None = None) -> bool:
         from ..._lib import api
         from ...core.stream import current_stream_handle as _st
         if add_ptr is not None:
@@ -101,6 +104,7 @@ class PostNormBlock:
             base, parts, inv, wts, top = self.mlp.forward(ctx, x, y)
             api.combine_layernorm_f32(base, None, parts, inv, wts, top, self.norm2[0].device_ptr,
                                       self.norm2[1].device_ptr, self.eps, x.device_ptr, T, W, 1, _st())
+        return False
 
     @property
     def weight_bytes(self) -> int:
@@ -115,7 +119,8 @@ class ParallelBlock:
     x += s1 * mixer(h) + s2 * ff(h) with per-channel factors s1, s2 (layer scales; ones without them), then the optional
     per-layer token input.  The two scaled adds ride in the epilogues of the output projection and of the down projection
     (C += s * product), so the block adds no launch of its own beyond the norm.  `add_ptr`: rows added to x before the norm
-    and written back (the embedding output at the start of a loop pass) -- same launch."""
+    and written back (the embedding output at the start of a loop pass) -- same launch.  When the block ends with a token
+    input and another parallel block follows, that block's norm (and its add) ride in the token input's last launch."""
 
     def __init__(self, norm, mixer, mixer_scale: GPUArray, mlp, mlp_scale: "GPUArray | None", side=None):
         self.norm, self.mixer, self.mlp, self.side = norm, mixer, mlp, side
@@ -123,16 +128,22 @@ class ParallelBlock:
         if mlp is not None and mlp_scale is None:
             raise ValueError("ParallelBlock: the feed-forward needs its scale vector")
 
-    def forward(self, ctx, x: GPUArray, cache_index: int | None = None, add_ptr: int | None = None) -> None:
+    def forward(self, ctx, x: GPUArray, cache_index: int | None = None, add_ptr: int | None = None, normed: bool = False,
+                next_norm=None, next_add_ptr: int | None = None) -> bool:
+        """normed: ctx.buf.h already holds norm(x) (the block before wrote it, with `add_ptr` applied).  next_norm /
+        next_add_ptr: the norm (and the rows to add first) of the block that runs next; returns True when this block
+        has written that block's normed rows (only the token input's last launch can)."""
         T, W = ctx.T, x.shape[1]
         h = ctx.buf.h
-        self.norm.forward(x.device_ptr, h.device_ptr, T, W, add_ptr=add_ptr,
-                          sum_out_ptr=x.device_ptr if add_ptr is not None else None)
+        if not normed:
+            self.norm.forward(x.device_ptr, h.device_ptr, T, W, add_ptr=add_ptr,
+                              sum_out_ptr=x.device_ptr if add_ptr is not None else None)
         self.mixer.forward(ctx, h, x, cache_index, out_scale=self.mixer_scale.device_ptr)
         if self.mlp is not None:
             self.mlp.forward(ctx, h.device_ptr, x.device_ptr, out_scale=self.mlp_scale.device_ptr)
         if self.side is not None:
-            self.side.forward(ctx, x)
+            return self.side.forward(ctx, x, next_norm, next_add_ptr)
+        return False
 
     @property
     def weight_bytes(self) -> int:

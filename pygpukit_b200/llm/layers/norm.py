@@ -56,4 +56,17 @@ class RowNorm:
                                   self.eps, out_ptr, rows, width, 1 if accumulate else 0, _st())
 
 
+    def forward_seam(self, y_ptr: int, x_ptr: int, nxt: "RowNorm", h_ptr: int, rows: int, width: int,
+                     add_ptr: int | None = None) -> None:
+        """One launch for the seam between two pre-norm blocks: x += self(y); x += add (when given); h = nxt(x).  Both
+        norms must be RMS norms with the same eps."""
+        from ..._lib import api
+        from ...core.stream import current_stream_handle as _st
+        api.rms_norm_seam_f32(y_ptr, self.weight.device_ptr, self.offset, x_ptr, add_ptr, nxt.weight.device_ptr, nxt.offset,
+                              self.eps, h_ptr, rows, width, _st())
+
+    def fuses_with(self, nxt: "RowNorm | None") -> bool:
+        return nxt is not None and self.kind == "rmsnorm" and nxt.kind == "rmsnorm" and self.eps == nxt.eps
+
+
 __all__ = ["Norm", "RowNorm"]

@@ -162,15 +162,25 @@ class LayeredCausalModel:
         W, V = cfg.hidden_size, cfg.vocab_size
         b, T = ctx.buf, ctx.T
         x = b.x
-        api.embed_rows_f32(self.embed_tokens.device_ptr, self.embed_dt, ctx.tok_ptr, x.device_ptr, T, W, V, _st())
-        if self.embed_norm is not None:
-            self.embed_norm.forward(x.device_ptr, x.device_ptr, T, W)
-        if b.x0 is not None:                           # kept for the later passes of the loop
-            api.memcpy_d2d(b.x0.device_ptr, x.device_ptr, T * W * 4, _st())
+        en = self.embed_norm
+        if en is not None and en.kind == "rmsnorm":    # embedding rows, their norm and the copy kept for later loop passes
+            api.embed_norm_rows_f32(self.embed_tokens.device_ptr, self.embed_dt, ctx.tok_ptr, en.weight.device_ptr, en.offset,
+                                    en.eps, x.device_ptr, b.x0.device_ptr if b.x0 is not None else None, T, W, V, _st())
+        else:
+            api.embed_rows_f32(self.embed_tokens.device_ptr, self.embed_dt, ctx.tok_ptr, x.device_ptr, T, W, V, _st())
+            if en is not None:
+                en.forward(x.device_ptr, x.device_ptr, T, W)
+            if b.x0 is not None:
+                api.memcpy_d2d(b.x0.device_ptr, x.device_ptr, T * W * 4, _st())
+        normed, hook = False, self.trace_hook
         for run, (li, add_first) in enumerate(self.runs):
-            self.blocks[li].forward(ctx, x, run, b.x0.device_ptr if add_first else None)
-            if self.trace_hook is not None:
-                self.trace_hook(run, x.to_numpy()[:T].copy())
+            nxt = self.runs[run + 1] if run + 1 < len(self.runs) else None
+            # the block may hand the next one its normed rows (not while a hook wants to see x between the two)
+            next_norm = self.blocks[nxt[0]].norm if nxt is not None and hook is None else None
+            normed = self.blocks[li].forward(ctx, x, run, b.x0.device_ptr if add_first and not normed else None, normed, next_norm,
+                                             b.x0.device_ptr if nxt is not None and nxt[1] else None)
+            if hook is not None:
+                hook(run, x.to_numpy()[:T].copy())
         if ctx.n_want:
             n = ctx.n_want
             xn = b.y                                   # free after the last block

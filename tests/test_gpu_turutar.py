@@ -83,6 +83,29 @@ def test_rms_norm_rows_offset_gather_sum_and_accumulate(W):
     assert np.abs(xs.to_numpy() - R.rms_norm(x + add, w, 1e-5, 1.0)).max() < 1e-5
 
 
+@pytest.mark.parametrize("W", [40, 1030])
+def test_seam_of_two_norms_and_embedding_with_its_norm(W):
+    rng = np.random.default_rng(W + 1)
+    n = 6
+    y, x, add = (rng.standard_normal((n, W)) for _ in range(3))
+    w1, w2 = 0.5 + 0.2 * rng.standard_normal(W), 0.3 * rng.standard_normal(W)
+    for extra in (None, add):
+        xs, h = f32(x), gk.zeros((n, W), gk.float32)
+        api.rms_norm_seam_f32(f32(y).device_ptr, f32(w1).device_ptr, 0.0, xs.device_ptr, f32(extra).device_ptr if extra is not None else None,
+                              f32(w2).device_ptr, 1.0, 1e-5, h.device_ptr, n, W, None)
+        want = x + R.rms_norm(y, w1, 1e-5) + (extra if extra is not None else 0.0)
+        assert np.abs(xs.to_numpy() - want).max() < 1e-5
+        assert np.abs(h.to_numpy() - R.rms_norm(want, w2, 1e-5, 1.0)).max() < 1e-5
+    table = bf16_round(rng.standard_normal((11, W)))
+    toks = [3, 10, 0, 3]
+    for wdt in (0, 2):
+        xs, keep_ = gk.zeros((4, W), gk.float32), gk.zeros((4, W), gk.float32)
+        api.embed_norm_rows_f32(dev_w(table, wdt).device_ptr, wdt, i32(toks).device_ptr, f32(w2).device_ptr, 1.0, 1e-5, xs.device_ptr,
+                                keep_.device_ptr, 4, W, 11, None)
+        assert np.abs(xs.to_numpy() - R.rms_norm(table[toks], w2, 1e-5, 1.0)).max() < 1e-5
+        assert np.array_equal(xs.to_numpy(), keep_.to_numpy())
+
+
 @pytest.mark.parametrize("wdt", [0, 2])
 @pytest.mark.parametrize("M", [3, 70])
 def test_gemm_epilogues_clamped_gate_scaled_accumulate_and_gathered_gelu(M, wdt):
